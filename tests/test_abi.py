@@ -25,19 +25,6 @@ def test_library_exports_every_declared_symbol(gpu_lib):
     assert b"sm_100a" in gpu_lib.lib().lmrs_b200_version()
 
 
-def test_sass_contains_the_blackwell_copy_engine_path():
-    """The GEMV streams weights with cp.async.bulk (SASS UBLKCP) and contains IDP.4A integer dot products."""
-    import shutil
-    import subprocess
-    so = os.path.join(ROOT, "lm.rs_b200", "lmrs_b200", "liblmrs_b200.so")
-    cuobjdump = shutil.which("cuobjdump") or "/usr/local/cuda/bin/cuobjdump"
-    if not os.path.exists(cuobjdump):
-        pytest.skip("cuobjdump not available")
-    sass = subprocess.run([cuobjdump, "-sass", so], capture_output=True, text=True).stdout
-    assert "UBLKCP" in sass and "IDP.4A" in sass and "SYNCS" in sass
-    assert "sm_100a" in subprocess.run([cuobjdump, "-lelf", so], capture_output=True, text=True).stdout
-
-
 @pytest.mark.skipif(os.path.exists("/dev/nvidia0"), reason="GPU present: the no-GPU failure path cannot be exercised")
 def test_no_gpu_means_loud_failure_not_fallback(gpu_lib, lf):
     buf = lf.write_synthetic(lf.model_args("tiny-llama", 1))
@@ -45,20 +32,6 @@ def test_no_gpu_means_loud_failure_not_fallback(gpu_lib, lf):
         gpu_lib.Transformer.new(buf)
     with pytest.raises(gpu_lib.LmrsError):
         gpu_lib.functional.softmax(np.zeros(4, np.float32))
-
-
-def test_sass_contains_the_cluster_and_tensor_core_paths():
-    """Decode attention pushes scores between the CTAs of a cluster with st.async (SASS STAS) and stages K/V with
-    cp.async (LDGSTS); the prefill GEMM issues tcgen05 int8 MMAs (UTCIMMA) fed by 2-D TMA loads (UTMALDG)."""
-    import shutil
-    import subprocess
-    so = os.path.join(ROOT, "lm.rs_b200", "lmrs_b200", "liblmrs_b200.so")
-    cuobjdump = shutil.which("cuobjdump") or "/usr/local/cuda/bin/cuobjdump"
-    if not os.path.exists(cuobjdump):
-        pytest.skip("cuobjdump not available")
-    sass = subprocess.run([cuobjdump, "-sass", so], capture_output=True, text=True).stdout
-    for mnemonic in ("STAS", "LDGSTS", "UCGABAR_ARV", "UTCIMMA", "UTMALDG", "LDTM"):
-        assert mnemonic in sass, mnemonic
 
 
 def test_compiled_caller_links_against_the_c_abi_and_fails_loudly_without_a_gpu(lf, tmp_path):
