@@ -1,0 +1,550 @@
+// dense_ops.cuh -- kernels for models with unquantized weights (bf16 or f32 operands, f32 accumulation): the building
+// blocks a folder-based architecture (arch.h) composes.  Every constant of a mechanism is a parameter, so that another
+// architecture can use the same kernel:
+//   embed_rows_kernel        token embedding + optional hashed bigram embedding of (previous token, token)
+//   rmsnorm_rows_kernel      x / sqrt(mean(x^2) + eps) * w per row, optional row gather, output in the operand type
+//   gemv_rows_kernel         one token row:  weights streamed once (HBM-bound), optional fused RMS-norm prologue,
+//                            epilogues: store*scale | x += ls * acc | act(gate) * up
+//   gemm_tiled_kernel        many rows, any shape, CUDA cores (the f32 path and ragged shapes); same epilogues
+//   qkv_post_kernel          per head: unit RMS norm of q/k or partial rotary, value mixing with an earlier layer's
+//                            values, sigmoid head gate, K/V rows written to the cache
+//   attn_rows_kernel         causal softmax attention with score scale and tanh soft-cap, grouped query heads, query
+//                            tile x KV head per CTA, optional split over the keys (decode) + attn_combine_kernel
+// What the design wants in 32-bit (norms, scores, softmax, residual, angles) is 32-bit here in both operand types.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "step_params.h"
+
+namespace lmrs {
+namespace dense {
+
+#define DN_DEVINL __device__ __forceinline__
+
+DN_DEVINL float to_f(float v) { return v; }
+DN_DEVINL float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+DN_DEVINL void from_f(float& d, float v) { d = v; }
+DN_DEVINL void from_f(__nv_bfloat16& d, float v) { d = __float2bfloat16_rn(v); }
+
+DN_DEVINL float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+DN_DEVINL float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// sum over the block (blockDim.x a multiple of 32, <= 1024); every thread gets the result; `red` = 33 floats of smem
+DN_DEVINL float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nw ? red[lane] : 0.0f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    const float r = red[32];
+    __syncthreads();
+    return r;
+}
+
+// position of row 0 of a step: a host constant, or read from the device-resident step parameters (decode graphs)
+struct PosSrc {
+    const StepParams* sp;
+    uint32_t pos;
+};
+DN_DEVINL uint32_t pos_of(const PosSrc& s) { return s.sp ? s.sp->pos : s.pos; }
+
+// ---- embedding -----------------------------------------------------------------------------------------------------
+// x[t] = embed[token] + bigram[(prev * mul_prev + token * mul_cur) mod buckets]; the first token of a sequence takes the
+// extra row `buckets`.  The token history lives on the device (tokens[position]): the previous token of a portion's
+// first row is whatever the previous step left there.
+template <typename WT> struct EmbedRowsParams {
+    const WT* embed; const WT* bigram;   // bigram may be null
+    uint32_t* tokens;                    // [max_tokens] history, rows pos .. pos+T-1 already filled for sp == null
+    float* x; int width;
+    PosSrc ps;
+    uint32_t buckets, mul_prev, mul_cur;
+};
+template <typename WT> __global__ void __launch_bounds__(128) embed_rows_kernel(const EmbedRowsParams<WT> p) {
+    const uint32_t t = blockIdx.x, pos = pos_of(p.ps) + t;
+    uint32_t tok;
+    if (p.ps.sp) { tok = p.ps.sp->token; if (threadIdx.x == 0) p.tokens[pos] = tok; }
+    else tok = p.tokens[pos];
+    const WT* e = p.embed + (size_t)tok * p.width;
+    const WT* b = nullptr;
+    if (p.bigram) {
+        uint32_t row = p.buckets;
+        if (pos > 0) {
+            const uint32_t prev = p.tokens[pos - 1];
+            row = (uint32_t)(((unsigned long long)prev * p.mul_prev + (unsigned long long)tok * p.mul_cur) % p.buckets);
+        }
+        b = p.bigram + (size_t)row * p.width;
+    }
+    float* x = p.x + (size_t)t * p.width;
+    for (int c = threadIdx.x; c < p.width; c += blockDim.x) x[c] = to_f(e[c]) + (b ? to_f(b[c]) : 0.0f);
+}
+
+// ---- RMS norm of rows -----------------------------------------------------------------------------------------------
+template <typename AT> struct NormRowsParams {
+    const float* x; int ldx;
+    const uint32_t* rows;   // optional gather: output row r reads input row rows[r]
+    const float* w;         // may be null (unit norm)
+    AT* out; int ldo;
+    int n; float eps;
+};
+template <typename AT> __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const NormRowsParams<AT> p) {
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const float* x = p.x + (size_t)(p.rows ? p.rows[r] : (uint32_t)r) * p.ldx;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < p.n; c += blockDim.x) { const float v = x[c]; ss += v * v; }
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)p.n + p.eps);
+    AT* o = p.out + (size_t)r * p.ldo;
+    for (int c = threadIdx.x; c < p.n; c += blockDim.x) from_f(o[c], p.w ? x[c] * inv * p.w[c] : x[c] * inv);
+}
+
+// ---- epilogues shared by the matrix kernels ---------------------------------------------------------------------------
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_GLU = 2 };
+template <typename AT> struct EpiParams {
+    float* out; int ldo;      // EPI_STORE: out = acc * scale;  EPI_RESID: out += ls[o] * acc
+    float scale;
+    const float* ls;
+    AT* act; int lda;         // EPI_GLU: act = silu(gate) * up in the operand type
+};
+DN_DEVINL float silu(float z) { return z / (1.0f + expf(-z)); }
+template <int EPI, typename AT> DN_DEVINL void epi_apply(const EpiParams<AT>& e, int t, int o, float a, float b) {
+    if (EPI == EPI_STORE) e.out[(size_t)t * e.ldo + o] = a * e.scale;
+    else if (EPI == EPI_RESID) e.out[(size_t)t * e.ldo + o] += e.ls[o] * a;
+    else from_f(e.act[(size_t)t * e.lda + o], silu(a) * b);
+}
+
+// ---- one row times a matrix: W [O][K] streamed once ----------------------------------------------------------------------
+// A warp owns output rows o = warp, warp + nwarps, ...; lanes walk K in 16-byte pieces, four pieces in flight per lane.
+// NORM: the input row is the f32 residual, normalised here (x * rsqrt(mean x^2 + eps) * nw) and rounded to the operand
+// type exactly as rmsnorm_rows_kernel does, so both routes feed the product the same numbers.
+template <typename AT, typename WT> struct GemvRowsParams {
+    const AT* a;              // [K] input row (NORM = false)
+    const float* x; const float* nw; float eps;   // NORM = true
+    const WT* w; const WT* w2;   // [O][K]; w2: the "up" matrix of EPI_GLU
+    int K, O;
+    EpiParams<AT> e;
+};
+template <typename WT> struct Vec16;
+template <> struct Vec16<float> { static constexpr int N = 4; };
+template <> struct Vec16<__nv_bfloat16> { static constexpr int N = 8; };
+template <typename WT> DN_DEVINL void load16(const WT* p, float (&v)[Vec16<WT>::N]);
+template <> DN_DEVINL void load16<float>(const float* p, float (&v)[4]) {
+    const float4 q = __ldcs(reinterpret_cast<const float4*>(p));
+    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+}
+template <> DN_DEVINL void load16<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 q = __ldcs(reinterpret_cast<const uint4*>(p));
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+}
+// NR weight rows against the same input row: the shared-memory reads of the input are paid once for NR rows
+template <typename WT, int NR>
+DN_DEVINL void dot_rows(const WT* const (&w)[NR], const float* __restrict__ xs, int K, int lane, bool vec, float (&out)[NR]) {
+    constexpr int N = Vec16<WT>::N;
+    float acc[NR];
+#pragma unroll
+    for (int r = 0; r < NR; r++) acc[r] = 0.0f;
+    if (vec) {
+        const int pieces = K / N;
+        int i = lane;
+        for (; i + 32 < pieces; i += 64) {
+            float v[NR][2][N];
+#pragma unroll
+            for (int r = 0; r < NR; r++) { load16<WT>(w[r] + (size_t)i * N, v[r][0]); load16<WT>(w[r] + (size_t)(i + 32) * N, v[r][1]); }
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                float xv[N];
+#pragma unroll
+                for (int j = 0; j < N; j += 4) {
+                    const float4 x4 = *reinterpret_cast<const float4*>(xs + (size_t)(i + 32 * u) * N + j);
+                    xv[j] = x4.x; xv[j + 1] = x4.y; xv[j + 2] = x4.z; xv[j + 3] = x4.w;
+                }
+#pragma unroll
+                for (int r = 0; r < NR; r++)
+#pragma unroll
+                    for (int j = 0; j < N; j++) acc[r] = fmaf(v[r][u][j], xv[j], acc[r]);
+            }
+        }
+        for (; i < pieces; i += 32) {
+            float xv[N];
+#pragma unroll
+            for (int j = 0; j < N; j += 4) {
+                const float4 x4 = *reinterpret_cast<const float4*>(xs + (size_t)i * N + j);
+                xv[j] = x4.x; xv[j + 1] = x4.y; xv[j + 2] = x4.z; xv[j + 3] = x4.w;
+            }
+#pragma unroll
+            for (int r = 0; r < NR; r++) {
+                float v0[N];
+                load16<WT>(w[r] + (size_t)i * N, v0);
+#pragma unroll
+                for (int j = 0; j < N; j++) acc[r] = fmaf(v0[j], xv[j], acc[r]);
+            }
+        }
+    } else {
+        for (int k = lane; k < K; k += 32)
+#pragma unroll
+            for (int r = 0; r < NR; r++) acc[r] = fmaf(to_f(w[r][k]), xs[k], acc[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < NR; r++) out[r] = warp_sum(acc[r]);
+}
+template <typename AT, typename WT, int EPI, bool NORM>
+__global__ void __launch_bounds__(256) gemv_rows_kernel(const GemvRowsParams<AT, WT> p) {
+    extern __shared__ __align__(16) float gv_xs[];   // [K rounded up to 4] the input row as f32, then 33 reduction slots
+    float* red = gv_xs + ((p.K + 3) & ~3);
+    if (NORM) {
+        float ss = 0.0f;
+        for (int c = threadIdx.x; c < p.K; c += blockDim.x) { const float v = p.x[c]; ss += v * v; }
+        ss = block_sum(ss, red);
+        const float inv = 1.0f / sqrtf(ss / (float)p.K + p.eps);
+        for (int c = threadIdx.x; c < p.K; c += blockDim.x) { AT r; from_f(r, p.x[c] * inv * p.nw[c]); gv_xs[c] = to_f(r); }
+    } else {
+        for (int c = threadIdx.x; c < p.K; c += blockDim.x) gv_xs[c] = to_f(p.a[c]);
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const bool vec = p.K % Vec16<WT>::N == 0;   // every weight row then starts on a 16-byte boundary
+    if (EPI == EPI_GLU) {
+        for (int o = blockIdx.x * nw + warp; o < p.O; o += gridDim.x * nw) {
+            const WT* const rows[2] = {p.w + (size_t)o * p.K, p.w2 + (size_t)o * p.K};
+            float r[2];
+            dot_rows<WT, 2>(rows, gv_xs, p.K, lane, vec, r);
+            if (lane == 0) epi_apply<EPI, AT>(p.e, 0, o, r[0], r[1]);
+        }
+    } else {
+        for (int o = 2 * (blockIdx.x * nw + warp); o < p.O; o += 2 * gridDim.x * nw) {
+            const int o1 = o + 1 < p.O ? o + 1 : o;
+            const WT* const rows[2] = {p.w + (size_t)o * p.K, p.w + (size_t)o1 * p.K};
+            float r[2];
+            dot_rows<WT, 2>(rows, gv_xs, p.K, lane, vec, r);
+            if (lane == 0) {
+                epi_apply<EPI, AT>(p.e, 0, o, r[0], 0.0f);
+                if (o1 != o) epi_apply<EPI, AT>(p.e, 0, o1, r[1], 0.0f);
+            }
+        }
+    }
+}
+
+// ---- many rows times a matrix on CUDA cores: out[T][O] = A[T][K] . W[O][K]^T, any shape --------------------------------
+// 64 x 64 output tile, K in steps of 16, 256 threads x (4 x 4) outputs; each output element adds its products in
+// ascending k, so a row's result does not depend on how many rows the call has.
+template <typename AT, typename WT> struct GemmTiledParams {
+    const AT* a; int lda;
+    const WT* w; const WT* w2;
+    int T, K, O;
+    EpiParams<AT> e;
+};
+template <typename AT, typename WT, int EPI>
+__global__ void __launch_bounds__(256) gemm_tiled_kernel(const GemmTiledParams<AT, WT> p) {
+    constexpr int BM = 64, BN = 64, BK = 16;
+    constexpr bool GLU = EPI == EPI_GLU;
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Ws[BK][BN + 4];
+    __shared__ float W2s[GLU ? BK : 1][BN + 4];
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    float acc[4][4] = {}, acc2[GLU ? 4 : 1][4] = {};
+    const int lr = threadIdx.x >> 2, lk = (threadIdx.x & 3) * 4;   // loader: row lr of the tile, k offset lk .. lk+3
+    for (int k0 = 0; k0 < p.K; k0 += BK) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int k = k0 + lk + j;
+            As[lk + j][lr] = (m0 + lr < p.T && k < p.K) ? to_f(p.a[(size_t)(m0 + lr) * p.lda + k]) : 0.0f;
+            Ws[lk + j][lr] = (n0 + lr < p.O && k < p.K) ? to_f(p.w[(size_t)(n0 + lr) * p.K + k]) : 0.0f;
+            if (GLU) W2s[lk + j][lr] = (n0 + lr < p.O && k < p.K) ? to_f(p.w2[(size_t)(n0 + lr) * p.K + k]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; k++) {
+            const float4 a4 = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+            const float4 w4 = *reinterpret_cast<const float4*>(&Ws[k][tx * 4]);
+            const float av[4] = {a4.x, a4.y, a4.z, a4.w}, wv[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+            if (GLU) {
+                const float4 u4 = *reinterpret_cast<const float4*>(&W2s[k][tx * 4]);
+                const float uv[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) acc2[GLU ? i : 0][j] = fmaf(av[i], uv[j], acc2[GLU ? i : 0][j]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int t = m0 + ty * 4 + i, o = n0 + tx * 4 + j;
+            if (t < p.T && o < p.O) epi_apply<EPI, AT>(p.e, t, o, acc[i][j], acc2[GLU ? i : 0][j]);
+        }
+}
+
+// ---- what happens to q, k, v (and the gate logits) between the projection and the attention ---------------------------
+// Input: one row per token of the fused projection [q (H*dk) | k (G*dk) | v (G*dv) | gate logits (H, optional)], f32.
+//   qk_mode QK_UNITNORM: every q and k head is divided by its root mean square (eps inside the root), no weight
+//   qk_mode QK_ROTARY:   the first rot_dims dimensions of every q and k head are rotated, dimension i paired with
+//                        i + rot_dims/2, by the angle position * f_i taken from host-made cos/sin tables [pos][rot_dims/2]
+//   v_mode  V_FIRST:     the values are also kept in v_first (this step's rows) for later layers
+//   v_mode  V_MIX:       v <- (1 - lambda) v + lambda v_first
+// q goes to q_out [T][H*dk], k and v to cache rows pos+t, sigmoid(gate logit) to gate_out [T][H].
+enum { QK_PLAIN = 0, QK_UNITNORM = 1, QK_ROTARY = 2 };
+enum { V_PLAIN = 0, V_FIRST = 1, V_MIX = 2 };
+struct QkvPostParams {
+    const float* qkv; int ld;
+    int H, G, dk, dv;
+    int qk_mode; float eps;
+    int rot_dims; const float* rot_cos; const float* rot_sin;   // [max_tokens][rot_dims/2]
+    int v_mode; float* v_first; const float* lambda;            // v_first [T][G*dv]; lambda: one float on the device
+    bool has_gate;
+    float* q_out; float* gate_out;
+    float* kcache; float* vcache;                               // [max_tokens][G*dk], [max_tokens][G*dv]
+    PosSrc ps;
+};
+__global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostParams p) {
+    const int t = blockIdx.x;
+    const uint32_t pos = pos_of(p.ps) + (uint32_t)t;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const float* row = p.qkv + (size_t)t * p.ld;
+    const int n_qk = p.H + p.G;
+    for (int task = warp; task < n_qk; task += nw) {   // q heads, then k heads
+        const bool is_q = task < p.H;
+        const float* src = row + (size_t)task * p.dk;  // k heads follow the q heads directly
+        float* dst = is_q ? p.q_out + ((size_t)t * p.H + task) * p.dk : p.kcache + ((size_t)pos * p.G + (task - p.H)) * p.dk;
+        if (p.qk_mode == QK_UNITNORM) {
+            float ss = 0.0f;
+            for (int d = lane; d < p.dk; d += 32) ss += src[d] * src[d];
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / (float)p.dk + p.eps);
+            for (int d = lane; d < p.dk; d += 32) dst[d] = src[d] * inv;
+        } else if (p.qk_mode == QK_ROTARY) {
+            const int half = p.rot_dims / 2;
+            const float* c = p.rot_cos + (size_t)pos * half;
+            const float* s = p.rot_sin + (size_t)pos * half;
+            for (int i = lane; i < half; i += 32) {
+                const float u = src[i], v = src[i + half];
+                dst[i] = u * c[i] - v * s[i];
+                dst[i + half] = v * c[i] + u * s[i];
+            }
+            for (int d = p.rot_dims + lane; d < p.dk; d += 32) dst[d] = src[d];
+        } else {
+            for (int d = lane; d < p.dk; d += 32) dst[d] = src[d];
+        }
+    }
+    const float* vsrc = row + (size_t)n_qk * p.dk;
+    const int nv = p.G * p.dv;
+    const float lam = p.v_mode == V_MIX ? *p.lambda : 0.0f;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+        float v = vsrc[i];
+        if (p.v_mode == V_FIRST) p.v_first[(size_t)t * nv + i] = v;
+        else if (p.v_mode == V_MIX) v = (1.0f - lam) * v + lam * p.v_first[(size_t)t * nv + i];
+        p.vcache[(size_t)pos * nv + i] = v;
+    }
+    if (p.has_gate)
+        for (int h = threadIdx.x; h < p.H; h += blockDim.x) p.gate_out[(size_t)t * p.H + h] = 1.0f / (1.0f + expf(-vsrc[nv + h]));
+}
+
+// ---- attention --------------------------------------------------------------------------------------------------------
+// score = (q . k) * scale, then softcap * tanh(score / softcap) when softcap > 0; row (t, head) sees keys 0 .. pos+t;
+// softmax in f32; output row times the head's gate (when given), written in the operand type as [T][H*dv].
+// CTA = (tile of TQ query tokens, KV head, chunk of HC query heads of that KV head[, key split]); 4 warps x RW row slots,
+// row slot r = (token r / HC, head r % HC).  Keys are walked in tiles of 64 staged in shared memory: lane j scores keys j
+// and j + 32 of the tile for each of its rows (K rows padded so that the 16-byte reads of 32 lanes do not collide), an
+// online softmax keeps (max, sum) per row, the probabilities go through shared memory and lane c accumulates output
+// columns c, c + 32, ... .  Tiles start at multiples of 64 keys whatever the portion, so a row's arithmetic does not
+// depend on how the prompt was cut.  With nsplit > 1 (decode) CTA `split` walks tiles split, split + nsplit, ... and writes
+// (max, sum, unnormalised row) to scratch for attn_combine_kernel.
+constexpr int ATT_KT = 64, ATT_WARPS = 4;
+template <typename AT> struct AttnRowsParams {
+    const float* q;           // [T][H*dk]
+    const float* kcache; const float* vcache;
+    const float* gate;        // [T][H] or null
+    AT* out;                  // [T][H*dv]
+    float* part;              // nsplit > 1: [T][H][nsplit][dv + 2]
+    int T, H, G, dk, dv, TQ, HC, nsplit;
+    float scale, softcap;
+    PosSrc ps;
+};
+inline int attn_k_stride(int dk) { const int d4 = (dk + 3) & ~3; return d4 + ((4 - d4 % 32) + 32) % 32; }   // == 4 mod 32
+template <int RW, int NI> inline size_t attn_smem_bytes(int dk, int dv) {
+    const int d4 = (dk + 3) & ~3, R = RW * ATT_WARPS;
+    return ((size_t)R * d4 + (size_t)ATT_KT * attn_k_stride(dk) + (size_t)ATT_KT * 32 * NI + (size_t)R * ATT_KT) * 4;
+}
+template <typename AT, int RW, int NI>
+__global__ void __launch_bounds__(ATT_WARPS * 32) attn_rows_kernel(const AttnRowsParams<AT> p) {
+    constexpr int R = RW * ATT_WARPS, DVP = 32 * NI;
+    extern __shared__ float at_sm[];
+    const int d4 = (p.dk + 3) & ~3, ks = d4 + ((4 - d4 % 32) + 32) % 32;
+    float* Qs = at_sm;                       // [R][d4]
+    float* Ks = Qs + (size_t)R * d4;         // [64][ks]
+    float* Vs = Ks + (size_t)ATT_KT * ks;    // [64][DVP]
+    float* Ps = Vs + (size_t)ATT_KT * DVP;   // [R][64]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int kv_mul = p.H / p.G;
+    const int chunks = (kv_mul + p.HC - 1) / p.HC;
+    const int g = blockIdx.y / chunks, h0 = (blockIdx.y % chunks) * p.HC;
+    const int t0 = blockIdx.x * p.TQ;
+    const int split = blockIdx.z;
+    const uint32_t pos0 = pos_of(p.ps);
+    // row slots
+    int r_t[RW], r_h[RW];
+    bool r_ok[RW];
+#pragma unroll
+    for (int i = 0; i < RW; i++) {
+        const int r = warp * RW + i;
+        r_t[i] = t0 + r / p.HC;
+        const int hl = h0 + r % p.HC;
+        r_h[i] = g * kv_mul + hl;
+        r_ok[i] = r / p.HC < p.TQ && r_t[i] < p.T && hl < kv_mul;
+    }
+    for (int e = threadIdx.x; e < R * d4; e += blockDim.x) {
+        const int r = e / d4, d = e - r * d4;
+        const int t = t0 + r / p.HC, hl = h0 + r % p.HC;
+        const bool ok = r / p.HC < p.TQ && t < p.T && hl < kv_mul && d < p.dk;
+        Qs[e] = ok ? p.q[((size_t)t * p.H + g * kv_mul + hl) * p.dk + d] : 0.0f;
+    }
+    const int t_last = min(p.T, t0 + p.TQ) - 1;
+    const int n_keys = (int)pos0 + t_last + 1;           // keys this CTA's last row sees
+    const int n_tiles = (n_keys + ATT_KT - 1) / ATT_KT;
+    float m[RW], l[RW], acc[RW][NI];
+#pragma unroll
+    for (int i = 0; i < RW; i++) {
+        m[i] = -1e30f; l[i] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < NI; c++) acc[i][c] = 0.0f;
+    }
+    const size_t krow = (size_t)p.G * p.dk, vrow = (size_t)p.G * p.dv;
+    for (int tile = split; tile < n_tiles; tile += p.nsplit) {
+        const int j0 = tile * ATT_KT;
+        __syncthreads();   // previous tile fully consumed (also orders the Qs fill before the first use)
+        for (int e = threadIdx.x; e < ATT_KT * d4; e += blockDim.x) {
+            const int j = e / d4, d = e - j * d4;
+            Ks[j * ks + d] = (j0 + j < n_keys && d < p.dk) ? p.kcache[(size_t)(j0 + j) * krow + (size_t)g * p.dk + d] : 0.0f;
+        }
+        for (int e = threadIdx.x; e < ATT_KT * DVP; e += blockDim.x) {
+            const int j = e / DVP, c = e - j * DVP;
+            Vs[e] = (j0 + j < n_keys && c < p.dv) ? p.vcache[(size_t)(j0 + j) * vrow + (size_t)g * p.dv + c] : 0.0f;
+        }
+        __syncthreads();
+        float s0[RW], s1[RW];
+#pragma unroll
+        for (int i = 0; i < RW; i++) { s0[i] = 0.0f; s1[i] = 0.0f; }
+        const float* k0p = Ks + (size_t)lane * ks;
+        const float* k1p = Ks + (size_t)(lane + 32) * ks;
+        for (int d = 0; d < d4; d += 4) {
+            const float4 ka = *reinterpret_cast<const float4*>(k0p + d);
+            const float4 kb = *reinterpret_cast<const float4*>(k1p + d);
+#pragma unroll
+            for (int i = 0; i < RW; i++) {
+                const float4 qv = *reinterpret_cast<const float4*>(Qs + (size_t)(warp * RW + i) * d4 + d);
+                s0[i] = fmaf(qv.x, ka.x, s0[i]); s0[i] = fmaf(qv.y, ka.y, s0[i]); s0[i] = fmaf(qv.z, ka.z, s0[i]); s0[i] = fmaf(qv.w, ka.w, s0[i]);
+                s1[i] = fmaf(qv.x, kb.x, s1[i]); s1[i] = fmaf(qv.y, kb.y, s1[i]); s1[i] = fmaf(qv.z, kb.z, s1[i]); s1[i] = fmaf(qv.w, kb.w, s1[i]);
+            }
+        }
+        float corr[RW];
+#pragma unroll
+        for (int i = 0; i < RW; i++) {
+            const int last = (int)pos0 + r_t[i];   // last visible key of this row
+            float a = s0[i] * p.scale, b = s1[i] * p.scale;
+            if (p.softcap > 0.0f) { a = p.softcap * tanhf(a / p.softcap); b = p.softcap * tanhf(b / p.softcap); }
+            const bool va = r_ok[i] && j0 + lane <= last, vb = r_ok[i] && j0 + lane + 32 <= last;
+            a = va ? a : -1e30f; b = vb ? b : -1e30f;
+            const float mt = warp_max(fmaxf(a, b));
+            const float mn = fmaxf(m[i], mt);
+            const float pa = va ? expf(a - mn) : 0.0f, pb = vb ? expf(b - mn) : 0.0f;
+            corr[i] = expf(m[i] - mn);
+            l[i] = l[i] * corr[i] + warp_sum(pa + pb);
+            m[i] = mn;
+            Ps[(size_t)(warp * RW + i) * ATT_KT + lane] = pa;
+            Ps[(size_t)(warp * RW + i) * ATT_KT + lane + 32] = pb;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < RW; i++)
+#pragma unroll
+            for (int c = 0; c < NI; c++) acc[i][c] *= corr[i];
+        for (int j = 0; j < ATT_KT; j += 4) {
+            float vv[4][NI];
+#pragma unroll
+            for (int jj = 0; jj < 4; jj++)
+#pragma unroll
+                for (int c = 0; c < NI; c++) vv[jj][c] = Vs[(size_t)(j + jj) * DVP + c * 32 + lane];
+#pragma unroll
+            for (int i = 0; i < RW; i++) {
+                const float4 pv = *reinterpret_cast<const float4*>(Ps + (size_t)(warp * RW + i) * ATT_KT + j);
+#pragma unroll
+                for (int c = 0; c < NI; c++) {
+                    acc[i][c] = fmaf(pv.x, vv[0][c], acc[i][c]); acc[i][c] = fmaf(pv.y, vv[1][c], acc[i][c]);
+                    acc[i][c] = fmaf(pv.z, vv[2][c], acc[i][c]); acc[i][c] = fmaf(pv.w, vv[3][c], acc[i][c]);
+                }
+            }
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int i = 0; i < RW; i++) {
+        if (!r_ok[i]) continue;
+        if (p.nsplit > 1) {
+            float* dst = p.part + (((size_t)r_t[i] * p.H + r_h[i]) * p.nsplit + split) * (p.dv + 2);
+            if (lane == 0) { dst[0] = m[i]; dst[1] = l[i]; }
+#pragma unroll
+            for (int c = 0; c < NI; c++)
+                if (c * 32 + lane < p.dv) dst[2 + c * 32 + lane] = acc[i][c];
+        } else {
+            const float gt = p.gate ? p.gate[(size_t)r_t[i] * p.H + r_h[i]] : 1.0f;
+            const float inv = gt / l[i];
+            AT* dst = p.out + ((size_t)r_t[i] * p.H + r_h[i]) * p.dv;
+#pragma unroll
+            for (int c = 0; c < NI; c++)
+                if (c * 32 + lane < p.dv) from_f(dst[c * 32 + lane], acc[i][c] * inv);
+        }
+    }
+}
+// merges the key splits of a row: one warp per (token, head)
+template <typename AT> struct AttnCombineParams {
+    const float* part; const float* gate; AT* out;
+    int rows, H, dv, nsplit;   // rows = T * H
+};
+template <typename AT> __global__ void __launch_bounds__(128) attn_combine_kernel(const AttnCombineParams<AT> p) {
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= p.rows) return;
+    const float* src = p.part + (size_t)r * p.nsplit * (p.dv + 2);
+    float mx = -1e30f;
+    for (int s = 0; s < p.nsplit; s++) mx = fmaxf(mx, src[(size_t)s * (p.dv + 2)]);
+    float l = 0.0f;
+    for (int s = 0; s < p.nsplit; s++) l += src[(size_t)s * (p.dv + 2) + 1] * expf(src[(size_t)s * (p.dv + 2)] - mx);
+    const float gt = p.gate ? p.gate[r] : 1.0f;
+    for (int c = lane; c < p.dv; c += 32) {
+        float a = 0.0f;
+        for (int s = 0; s < p.nsplit; s++) a += src[(size_t)s * (p.dv + 2) + 2 + c] * expf(src[(size_t)s * (p.dv + 2)] - mx);
+        from_f(p.out[(size_t)r * p.dv + c], a * (gt / l));
+    }
+}
+
+// f32 <- bf16 widening of a weight tensor (the f32 operand mode keeps its weights as f32 in HBM)
+__global__ void widen_bf16_kernel(float* dst, const __nv_bfloat16* src, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) dst[i] = __bfloat162float(src[i]);
+}
+
+}  // namespace dense
+}  // namespace lmrs

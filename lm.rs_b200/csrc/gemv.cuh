@@ -31,6 +31,7 @@
 // boundary.  Plain mode (operator ABI, batched prefill rows, NCCL-sharded steps): f32 arrays + griddepcontrol.wait.
 #pragma once
 #include "common.cuh"
+#include "step_params.h"
 #include "exact_math.cuh"
 
 namespace lmrs {
@@ -42,12 +43,6 @@ constexpr int NORM_MAX_DIM = 4096;  // PRO_NORM keeps the vector in registers: d
 enum { PRO_NORM = 0, PRO_QUANT = 1, PRO_RAW = 2 };
 enum { EPI_STORE = 0, EPI_QKV = 1, EPI_GLU_SILU = 2, EPI_GLU_GELU = 3, EPI_LOGITS = 4 };
 
-struct StepParams {
-    uint32_t token;      // decode: token id; serial prefill: row index into the staged embeddings
-    uint32_t pos;        // position of this step
-    uint32_t mask_base;  // Gemma window quirk: the reference tests `pos - t` with the BATCH start pos
-    uint32_t seq;        //   (src/transformer.rs:525); decode passes pos.  seq: launch number (grid-barrier base)
-};
 
 struct GemvParams {
     const uint8_t* wq_a; const float* ws_a;   // matrix A: block-packed (BP16) weights; ws_* unused (scales ride in the blocks)

@@ -23,6 +23,7 @@
 #include "prefill_attn.cuh"
 #include "f32_ops.cuh"
 #include "shard.h"
+#include "arch.h"
 
 #include <map>
 
@@ -129,6 +130,10 @@ struct lmrs_b200 {
     bool use_graph = true, use_pdl = true;
     int gemv_cfg = 0, gemv_ctas_per_sm = 1;
     int l2pf = 0, l2pf_cls_mb = 24, l2pf_chunk = 32768, l2pf_ef = 1;   // L2 prefetch of upcoming weights during the attention phase (make_phases)
+    // a folder-based architecture (arch.h) behind this handle: the step, sampling and generate entry points below drive it
+    // instead of the LMRS phase chain; args describes it, d_logits / d_step / the sampler buffers are shared
+    ArchModel* arch = nullptr;
+    float* d_want = nullptr; size_t want_cap = 0;     // logits of the wanted rows of a forward_tokens call (device)
     Shard shard;  // multi-GPU bootstrap / NCCL fallback (shard.h); inert when world == 1
     // peer exchange (common.cuh, N-GPU mode): ONE cudaMalloc'ed block per GPU, mapped into every peer through CUDA IPC:
     //   [n_layers][2][world][dim] LL words (slot r of a vector = rank r's partial) | flags | logits[vocab] |
@@ -1424,6 +1429,8 @@ extern "C" void lmrs_b200_destroy(lmrs_b200_t* m) {
     }
     cudaSetDevice(m->device);
     if (m->own_stream) cudaStreamSynchronize(m->own_stream);
+    if (m->arch) { m->d_logits = nullptr; delete m->arch; m->arch = nullptr; }   // the model owns its logits buffer
+    cudaFree(m->d_want);
     for (int v = 0; v < 8; v++) {
         if (m->g_decode[v]) cudaGraphExecDestroy(m->g_decode[v]);
         if (m->g_prefill[v]) cudaGraphExecDestroy(m->g_prefill[v]);
@@ -1451,6 +1458,110 @@ extern "C" void lmrs_b200_destroy(lmrs_b200_t* m) {
     delete m;
 }
 
+// ---- models that come as a folder (config.json + model.safetensors): arch.h ----------------------------------------------
+namespace lmrs { void register_genetar(); }
+static void register_architectures() {
+    static bool done = false;
+    if (done) return;
+    done = true;
+    register_genetar();
+}
+static int open_arch(const char* dir, int device, int dtype, uint32_t max_tokens, lmrs_b200_t** out) {
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0)
+        return fail("lmrs_b200: no CUDA device available (this library has no CPU fallback)");
+    if (device < 0) CK(cudaGetDevice(&device));
+    CK(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    CK(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(std::string("lmrs_b200: device '") + prop.name + "' is sm_" + std::to_string(prop.major) + std::to_string(prop.minor) +
+                    "; this library contains sm_100a code only");
+    register_architectures();
+    ArchOptions opt;
+    opt.dtype = dtype; opt.max_tokens = max_tokens; opt.device = device; opt.sms = prop.multiProcessorCount;
+    std::string err;
+    ArchModel* am = arch_open(dir, opt, err);
+    if (!am) return fail(err);
+    lmrs_b200* m = new lmrs_b200();
+    m->arch = am;
+    m->device = device;
+    m->sms = prop.multiProcessorCount;
+    m->use_pdl = false;   // the sampler kernel is an ordinary launch behind the model's kernels
+    lmrs_args_t& a = m->args;
+    a.dim = am->info.width; a.hidden_dim = am->info.ff; a.n_layers = am->info.n_layers; a.n_heads = am->info.heads;
+    a.head_size = am->info.head_dim; a.n_kv_heads = am->info.kv_heads; a.vocab_size = am->info.vocab; a.seq_len = am->info.max_tokens;
+    a.rms_norm_eps = am->info.eps; a.rope_theta = 0.0f; a.q_type = 0; a.model_type = 3; a.group_size = 0; a.multimodal = 0;
+    m->d_logits = am->d_logits;
+    auto bail = [&](cudaError_t e, const char* what) {
+        lmrs_b200_destroy(m);
+        return fail(std::string(what) + ": " + cudaGetErrorString(e));
+    };
+    cudaError_t e;
+    if ((e = cudaMalloc(&m->d_step, sizeof(StepParams))) != cudaSuccess) return bail(e, "cudaMalloc");
+    if ((e = cudaMalloc(&m->d_amax, 256 * 4)) != cudaSuccess || (e = cudaMalloc(&m->d_aidx, 256 * 4)) != cudaSuccess ||
+        (e = cudaMalloc(&m->d_ticket, 4)) != cudaSuccess || (e = cudaMemset(m->d_ticket, 0, 4)) != cudaSuccess ||
+        (e = cudaMalloc(&m->d_next, 4)) != cudaSuccess)
+        return bail(e, "cudaMalloc");
+    if ((e = cudaMallocHost(&m->h_step_ring, sizeof(StepParams) * 64)) != cudaSuccess ||
+        (e = cudaMallocHost(&m->h_logits, (size_t)a.vocab_size * 4)) != cudaSuccess)
+        return bail(e, "cudaMallocHost");
+    if ((e = cudaStreamCreateWithFlags(&m->own_stream, cudaStreamNonBlocking)) != cudaSuccess) return bail(e, "cudaStreamCreate");
+    m->stream = m->own_stream;
+    *out = m;
+    return 0;
+}
+extern "C" int lmrs_b200_open(const char* path, int device, int dtype, uint32_t max_tokens, lmrs_b200_t** out) {
+    if (!path || !out) return fail("null argument");
+    if (dtype != 0 && dtype != 1) return fail("dtype: 0 = bfloat16 operands, 1 = float32");
+    if (arch_is_model_dir(path)) return open_arch(path, device, dtype, max_tokens, out);
+    if (dtype != 0) return fail("LMRS files hold quantized weights: they run in their own number format only (dtype 0)");
+    FILE* f = fopen(path, "rb");
+    if (!f) return fail(std::string("cannot open ") + path);
+    std::vector<uint8_t> buf;
+    fseek(f, 0, SEEK_END);
+    const long len = ftell(f);
+    fseek(f, 0, SEEK_SET);
+    if (len > 0) { buf.resize((size_t)len); if (fread(buf.data(), 1, (size_t)len, f) != (size_t)len) { fclose(f); return fail(std::string("cannot read ") + path); } }
+    fclose(f);
+    size_t end = 0;
+    return create_common(buf.data(), buf.size(), device, 0, 1, nullptr, out, &end);
+}
+static int step_one(lmrs_b200* m, bool with_params, uint32_t token, uint32_t pos);
+extern "C" int lmrs_b200_forward_tokens(lmrs_b200_t* m, const uint32_t* tokens, size_t n, uint32_t pos, const uint32_t* want,
+                                        size_t n_want, float* logits_out) {
+    if (!m || (n && !tokens) || (n_want && (!want || !logits_out))) return fail("null argument");
+    if ((size_t)pos + n > m->args.seq_len) return fail("position out of range");
+    CK(cudaSetDevice(m->device));
+    const size_t V = m->args.vocab_size;
+    if (m->arch) {
+        if (n_want * V > m->want_cap) {
+            cudaFree(m->d_want); m->d_want = nullptr; m->want_cap = 0;
+            CK(cudaMalloc(&m->d_want, n_want * V * 4));
+            m->want_cap = n_want * V;
+        }
+        if (m->arch->forward_tokens(m->stream, tokens, n, pos, want, n_want, m->d_want)) return fail(m->arch->error);
+        if (n_want) CK(cudaMemcpyAsync(logits_out, m->d_want, n_want * V * 4, cudaMemcpyDeviceToHost, m->stream));
+        CK(cudaStreamSynchronize(m->stream));
+        return 0;
+    }
+    // LMRS-file models: one decode step per token (their batched prefill produces no logits)
+    for (size_t i = 0; i < n; i++) {
+        if (lmrs_b200_forward_device(m, tokens[i], pos + (uint32_t)i)) return 1;
+        for (size_t k = 0; k < n_want; k++)
+            if (want[k] == i) CK(cudaMemcpyAsync(logits_out + k * V, m->d_logits, V * 4, cudaMemcpyDeviceToHost, m->stream));
+    }
+    CK(cudaStreamSynchronize(m->stream));
+    return 0;
+}
+extern "C" int lmrs_b200_set_option(lmrs_b200_t* m, const char* name, int value) {
+    if (!m || !name) return fail("null argument");
+    if (!m->arch) return fail("set_option: folder models only");
+    if (!strcmp(name, "keep_layers")) m->arch->set_keep_layer_outputs(value != 0);
+    else m->arch->set_option(name, value);
+    return 0;
+}
+
 extern "C" int lmrs_b200_args(const lmrs_b200_t* m, lmrs_args_t* out) {
     if (!m || !out) return fail("null argument");
     *out = m->args;
@@ -1461,6 +1572,7 @@ static int step_one(lmrs_b200* m, bool with_params, uint32_t token, uint32_t pos
     CK(cudaSetDevice(m->device));
     if (with_params) { if (push_step(m, token, pos, pos)) return 1; }
     else next_seq(m);   // the device advanced (token, pos, seq) itself: keep the host's sequence counter in step
+    if (m->arch) return m->arch->decode_enqueue(m->stream, m->d_step, pos) ? fail(m->arch->error) : 0;
     const int v = m->att_variant = attn_variant_for(m, pos);
     return run_graph(m, &m->g_decode[v], &m->g_decode_stream[v], &m->n_decode_kernels[v], true);
 }
@@ -1552,6 +1664,7 @@ extern "C" int lmrs_b200_generate_greedy(lmrs_b200_t* m, uint32_t first_token, u
 
 extern "C" int lmrs_b200_bench_gemv_pass(lmrs_b200_t* m, uint32_t pos, int* n_launches) {
     if (!m) return fail("null handle");
+    if (m->arch) return fail("this entry point serves LMRS-file models only; folder models take tokens: lmrs_b200_forward_tokens");
     if (pos >= m->args.seq_len) return fail("position out of range");
     for (lmrs_b200* g : members(m)) {
         CK(cudaSetDevice(g->device));
@@ -1565,6 +1678,7 @@ extern "C" int lmrs_b200_bench_gemv_pass(lmrs_b200_t* m, uint32_t pos, int* n_la
 
 extern "C" int lmrs_b200_bench_attn_pass(lmrs_b200_t* m, uint32_t pos, int* n_launches) {
     if (!m) return fail("null handle");
+    if (m->arch) return fail("this entry point serves LMRS-file models only; folder models take tokens: lmrs_b200_forward_tokens");
     if (pos >= m->args.seq_len) return fail("position out of range");
     CK(cudaSetDevice(m->device));
     if (push_step(m, 0, pos, pos)) return 1;
@@ -1596,6 +1710,7 @@ extern "C" int lmrs_b200_synchronize(lmrs_b200_t* m) {
 }
 extern "C" int lmrs_b200_kernel_launches(const lmrs_b200_t* m, uint64_t* count) {
     if (!m || !count) return fail("null argument");
+    if (m->arch) { *count = m->launches + m->arch->launches; return 0; }
     *count = 0;
     for (lmrs_b200* g : members(const_cast<lmrs_b200*>(m))) *count += g->launches;   // a group counts the kernels of all its GPUs
     return 0;
@@ -1604,6 +1719,7 @@ extern "C" int lmrs_b200_kernel_launches(const lmrs_b200_t* m, uint64_t* count) 
 extern "C" int lmrs_b200_get_embeddings(const lmrs_b200_t* cm, const uint32_t* tokens, size_t n, float* out) {
     lmrs_b200* m = const_cast<lmrs_b200*>(cm);
     if (!m || !tokens || !out) return fail("null argument");
+    if (m->arch) return fail("this entry point serves LMRS-file models only; folder models take tokens: lmrs_b200_forward_tokens");
     if (n == 0) return 0;
     for (size_t i = 0; i < n; i++)
         if (tokens[i] >= m->args.vocab_size) return fail("token out of range");
@@ -1627,6 +1743,7 @@ extern "C" int lmrs_b200_get_embeddings(const lmrs_b200_t* cm, const uint32_t* t
 
 extern "C" int lmrs_b200_fill_kv_cache(lmrs_b200_t* m, float* emb, size_t n_floats, uint32_t pos, uint32_t* new_pos) {
     if (!m || !emb || !new_pos) return fail("null argument");
+    if (m->arch) return fail("this entry point serves LMRS-file models only; folder models take tokens: lmrs_b200_forward_tokens");
     const size_t dim = m->args.dim;
     const size_t n = n_floats / dim;
     if (pos + n > m->args.seq_len) return fail("position out of range (seq_len is clamped to 8192, src/transformer.rs:158)");
@@ -1701,6 +1818,10 @@ extern "C" int lmrs_b200_last_prefill_device_ms(const lmrs_b200_t* m, float* ms)
 
 extern "C" int lmrs_b200_read_kv(lmrs_b200_t* m, uint32_t layer, uint32_t pos0, uint32_t n, float* k_out, float* v_out) {
     if (!m || !k_out || !v_out) return fail("null argument");
+    if (m->arch) {
+        CK(cudaSetDevice(m->device));
+        return m->arch->read_kv(m->stream, layer, pos0, n, k_out, v_out) ? fail(m->arch->error) : 0;
+    }
     if (layer >= m->args.n_layers || pos0 + n > m->args.seq_len) return fail("out of range");
     const std::vector<lmrs_b200*> grp = members(m);
     // a group returns whole rows [n][kv_dim] (GPU r holds columns [r * l_kv_dim, (r + 1) * l_kv_dim)); a single sharded
@@ -1722,6 +1843,13 @@ extern "C" int lmrs_b200_debug_buffer(lmrs_b200_t* m, const char* name, float* o
     if (!m || !name || !out || !n) return fail("null argument");
     const std::string nm(name);
     CK(cudaSetDevice(m->device));
+    if (m->arch) {   // folder models: "layers" = the residual stream after every layer of the last forward_tokens call
+        if (nm != "layers") return fail("folder models expose only the debug buffer 'layers'");
+        size_t got = 0;
+        if (m->arch->read_layer_outputs(m->stream, out, *n, &got)) return fail(m->arch->error);
+        *n = got;
+        return 0;
+    }
     if (nm == "trace_reset") {   // the device-side counter restarts with every launch
         CK(cudaStreamSynchronize(m->stream));
         if (m->d_trace) CK(cudaMemsetAsync(m->d_trace, 0, 2 * 8192 * 8, m->stream));

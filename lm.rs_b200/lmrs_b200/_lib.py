@@ -16,6 +16,7 @@ ABI_SYMBOLS = [
     "lmrs_b200_kernel_launches", "lmrs_b200_bench_gemv_pass", "lmrs_b200_bench_attn_pass", "lmrs_b200_last_prefill_device_ms", "lmrs_b200_read_kv", "lmrs_b200_debug_buffer", "lmrs_b200_matmul_q8", "lmrs_b200_matmul_q4", "lmrs_b200_matmul_f32", "lmrs_b200_matmul_rest",
     "lmrs_b200_quantize_q8", "lmrs_b200_quantize_q4", "lmrs_b200_rmsnorm", "lmrs_b200_softmax", "lmrs_b200_layernorm",
     "lmrs_b200_weights_upload", "lmrs_b200_matmul_w", "lmrs_b200_weights_free",
+    "lmrs_b200_open", "lmrs_b200_forward_tokens", "lmrs_b200_set_option",
     "lmrs_b200_last_error", "lmrs_b200_version",
 ]
 
@@ -31,7 +32,7 @@ class Args(C.Structure):
 
 def build(force: bool = False) -> str:
     """Compile liblmrs_b200.so in-tree with nvcc for sm_100a (cross-compiles without a GPU)."""
-    cmd = ["make", "-C", PKG_ROOT, "-s"] + (["-B"] if force else [])
+    cmd = ["make", "-C", PKG_ROOT, "-s", "-j4"] + (["-B"] if force else [])
     subprocess.check_call(cmd)
     return SO_PATH
 
@@ -86,6 +87,9 @@ def lib():
     L.lmrs_b200_matmul_w.argtypes = [vp, vp, vp, vp, i]
     L.lmrs_b200_weights_free.argtypes = [vp]
     L.lmrs_b200_weights_free.restype = None
+    L.lmrs_b200_open.argtypes = [C.c_char_p, i, i, u32, C.POINTER(vp)]
+    L.lmrs_b200_forward_tokens.argtypes = [vp, vp, sz, u32, vp, sz, vp]
+    L.lmrs_b200_set_option.argtypes = [vp, C.c_char_p, i]
     _lib = L
     return L
 

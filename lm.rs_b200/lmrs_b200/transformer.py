@@ -20,6 +20,7 @@ class ModelType(IntEnum):  # src/transformer.rs:50-55
     GEMMA = 0
     LLAMA = 1
     PHI = 2
+    GENETAR = 3   # a folder model (config.json + model.safetensors), not an LMRS file
 
 
 class QuantType(IntEnum):  # src/quantization.rs:1-6
@@ -67,6 +68,37 @@ class Transformer:
         a = Args()
         check(lib().lmrs_b200_args(h, C.byref(a)))
         return cls(h, a, world=world), end.value
+
+    @classmethod
+    def open(cls, path: str, dtype: str = "bfloat16", max_tokens: int = 0, device: int = -1):
+        """An LMRS file, or a model folder (config.json + model.safetensors) whose architecture the library's registry
+        knows.  dtype "bfloat16" | "float32" chooses the operand format of a folder model."""
+        code = {"bfloat16": 0, "bf16": 0, "float32": 1, "f32": 1}.get(dtype)
+        if code is None:
+            raise LmrsError(f"unknown dtype {dtype!r}")
+        h = C.c_void_p()
+        check(lib().lmrs_b200_open(str(path).encode(), device, code, max_tokens, C.byref(h)))
+        a = Args()
+        check(lib().lmrs_b200_args(h, C.byref(a)))
+        return cls(h, a)
+
+    def forward_tokens(self, tokens, pos: int, want=()) -> np.ndarray:
+        """tokens at positions pos.. in one pass; returns the logits of the rows listed in `want`, [len(want)][vocab]."""
+        t = np.ascontiguousarray(tokens, dtype=np.uint32)
+        w = np.ascontiguousarray(want, dtype=np.uint32)
+        out = np.zeros((w.size, self.args.vocab_size), np.float32)
+        check(lib().lmrs_b200_forward_tokens(self._h, _vp(t), t.size, pos, _vp(w), w.size, _vp(out)))
+        return out
+
+    def set_option(self, name: str, value: int) -> None:
+        check(lib().lmrs_b200_set_option(self._h, name.encode(), int(value)))
+
+    def layer_outputs(self, n_tokens: int) -> np.ndarray:
+        """residual stream after every layer of the last forward_tokens call (set_option("keep_layers", 1) first)"""
+        cap = self.args.n_layers * n_tokens * self.args.dim
+        out, n = np.zeros(cap, np.float32), C.c_size_t(cap)
+        check(lib().lmrs_b200_debug_buffer(self._h, b"layers", _vp(out), C.byref(n)))
+        return out[: n.value].reshape(self.args.n_layers, n_tokens, self.args.dim)
 
     # -- the four methods of the drop-in boundary -------------------------------------------------------------
     def forward(self, token: int, pos: int) -> np.ndarray:
