@@ -138,6 +138,135 @@ def load_gemv_traffic(model, quant):
     return d["traffic_bytes_per_launch_avg"], "profiles/r2_gemv_traffic.json (ncu --set full, per-launch average)"
 
 
+def bench_arch(args):
+    """--arch genetar: the folder-model architecture and the closest LMRS model (Llama, Q8_0) at the same layer shape, one GPU.
+    Prefill: device time (CUDA events on the handle's stream) of one pass over T prompt tokens.  Decode: device time of K
+    HBM-resident steps at positions P.. after a P-token prompt, and the same loop end to end through forward_argmax.  Every
+    step streams the whole weight set (larger than L2), so no flush is needed between steps."""
+    import shutil
+    import tempfile
+    import torch
+    import lmrs_b200
+    from lmrs_b200 import lmrs_file as lf, model_dir as md
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (lmrs_b200 has no CPU fallback)")
+    torch.cuda.set_device(0)
+    overrides = {"n_layers": args.arch_layers} if args.arch_layers > 0 else {}
+    a = lf.model_args(args.model, 1, **overrides)
+    lens = [int(x) for x in args.arch_prefill.split(",") if x]
+    peak_hbm, peak_src = load_peaks()
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak_tf = float(json.load(f)["bf16_tflops"]); tf_src = "measured cuBLAS bf16 burst (MEASURED_PEAKS.json)"
+    except Exception:
+        peak_tf, tf_src = 1590.0, "fallback 1.59 PFLOP/s"
+    P, K, Wm = args.pos, args.steps, args.warmup
+    cap = max(lens + [P]) + K + Wm + 8
+    stream = torch.cuda.Stream()
+    sampler = ClockSampler(0); sampler.start()
+
+    def timed(fn, reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for _ in range(reps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    def decode_legs(m, vocab):
+        toks = np.random.default_rng(2).integers(0, vocab, Wm + K)
+        for i in range(Wm):
+            m.forward_device(int(toks[i]), P + (i % K))
+        torch.cuda.synchronize()
+        l0 = m.kernel_launches()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(K):
+            m.forward_device(int(toks[Wm + i]), P + i)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / K
+        launches = (m.kernel_launches() - l0) // K
+        tok = 1
+        for i in range(Wm):
+            tok = m.forward_argmax(tok, P + i)
+        t0 = time.perf_counter()
+        for i in range(K):
+            tok = m.forward_argmax(tok, P + i)
+        e2e_ms = (time.perf_counter() - t0) / K * 1e3
+        return ms, e2e_ms, launches
+
+    out = {}
+    # ---- the folder model ---------------------------------------------------------------------------------------------
+    cfg = md.genetar_config(a.dim, a.hidden_dim, a.n_layers, a.n_heads, a.n_kv_heads, a.head_size, a.vocab_size)
+    tmp = tempfile.mkdtemp(prefix="genetar_bench_")
+    try:
+        md.write_random_genetar(tmp, cfg, seed=0)
+        m = lmrs_b200.Transformer.open(tmp, dtype="bfloat16", max_tokens=cap)
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+    m.set_stream(stream.cuda_stream)
+    prompt = np.random.default_rng(1).integers(0, a.vocab_size, max(lens + [P]) + 1).astype(np.uint32)
+    flops_tok = md.genetar_matmul_flops_per_token(cfg) - 2 * a.vocab_size * a.dim   # the head runs on wanted rows only
+    pre = {}
+    for T in lens:
+        m.forward_tokens(prompt[:T], 0, [T - 1])
+        ms = timed(lambda: m.forward_tokens(prompt[:T], 0, [T - 1]), 3)
+        att = 4.0 * a.n_heads * a.head_size * T * (T + 1) / 2 * a.n_layers
+        fl = flops_tok * T + att
+        pre[str(T)] = {"ms": ms, "tok_s": T / ms * 1e3, "tflops": fl / ms / 1e9, "frac_of_bf16_peak": fl / ms / 1e9 / peak_tf,
+                       "matmul_flops": flops_tok * T, "attention_flops_f32": att}
+    m.forward_tokens(prompt[:P], 0, [])
+    ms, e2e_ms, launches = decode_legs(m, a.vocab_size)
+    kv = sum(2 * (P + K // 2) * L["mixer"]["kv_heads"] * L["mixer"]["dim"] * 4 for L in cfg["layers"])
+    by = md.genetar_param_bytes(cfg) + kv
+    out["genetar"] = {"dtype": "bf16 weights and operands, f32 accumulation, f32 KV cache", "weight_bytes": md.genetar_param_bytes(cfg),
+                      "prefill": pre, "decode": {"ms_per_step": ms, "tok_s": 1e3 / ms, "e2e_tok_s": 1e3 / e2e_ms, "launches_per_step": launches,
+                                                 "algorithmic_bytes_per_step": by, "gb_s": by / ms / 1e6, "frac_of_hbm_peak": by / ms / 1e6 / peak_hbm}}
+    gl = m.kernel_launches()
+    m.close()
+    # ---- the closest LMRS model: Llama, Q8_0, same shape ----------------------------------------------------------------------
+    buf = lf.write_synthetic(a, seed=0, mode="fast")
+    m, _ = lmrs_b200.Transformer.new(buf, 0)
+    pre = {}
+    for T in lens:
+        if T > a.seq_len:
+            continue
+        emb0 = m.get_embeddings(prompt[:T])
+        for _ in range(2):
+            emb = emb0.copy()
+            m.fill_kv_cache(emb, 0)
+        ms = m.last_prefill_device_ms()
+        ops = lf.prefill_int8_ops(a, T)
+        pre[str(T)] = {"ms": ms, "tok_s": T / ms * 1e3, "tops_int8": ops / ms / 1e9, "frac_of_nominal_int8_peak": ops / ms / 1e9 / 4500.0}
+    emb = m.get_embeddings(prompt[:P])
+    m.fill_kv_cache(emb, 0)
+    m.set_stream(stream.cuda_stream)
+    ms, e2e_ms, launches = decode_legs(m, a.vocab_size)
+    by = lf.decode_bytes_per_token(a, P + K // 2)
+    out["llama_q8"] = {"dtype": "int8 x int8 -> int32 groups, f32 accumulate, f32 KV cache", "weight_bytes": lf.decode_bytes_per_token(a),
+                       "prefill": pre, "decode": {"ms_per_step": ms, "tok_s": 1e3 / ms, "e2e_tok_s": 1e3 / e2e_ms, "launches_per_step": launches,
+                                                  "algorithmic_bytes_per_step": by, "gb_s": by / ms / 1e6, "frac_of_hbm_peak": by / ms / 1e6 / peak_hbm}}
+    gl += m.kernel_launches()
+    m.set_stream(0)
+    m.close()
+    clocks = sampler.stop()
+    g = out["genetar"]["decode"]
+    print(json.dumps({
+        "metric": f"decode tok/s Genetar bf16 at the layer shape of {args.model} (prefill and the Q8_0 Llama of the same shape in 'arch')",
+        "value": g["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": Wm, "ms_per_step": g["ms_per_step"],
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"model": f"Genetar {a.n_layers} layers, width {a.dim}, ff {a.hidden_dim}, {a.n_heads}/{a.n_kv_heads} heads of {a.head_size}, vocab {a.vocab_size}",
+                   "first_pos": P, "batch": 1, "prefill_lengths": lens,
+                   "l2": "inputs larger than L2 (whole weight set streamed every step); no flush needed"},
+        "e2e": {"value": g["e2e_tok_s"], "unit": "tok/s", "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 4,
+                "api": "forward_argmax(token, pos) -> next token"},
+        "gpu_launches": gl, "clocks": clocks, "peaks": {"hbm_gb_s": peak_hbm, "hbm_source": peak_src, "bf16_tflops": peak_tf, "bf16_source": tf_src},
+        "arch": out}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -149,8 +278,15 @@ def main():
     ap.add_argument("--pos", type=int, default=512, help="prompt length / first decode position")
     ap.add_argument("--cpu-steps", type=int, default=16, help="decode steps of the bounded cpu_baseline sample")
     ap.add_argument("--parity-steps", type=int, default=4, help="greedy decode steps replayed on the CPU oracle (0: skip the parity block)")
+    ap.add_argument("--arch", default="", choices=["", "genetar"],
+                    help="instead of the default workload: prefill and decode throughput of this folder-model architecture (random "
+                         "bf16 weights at the layer shape of --model) beside the LMRS Q8_0 Llama of the same shape")
+    ap.add_argument("--arch-layers", type=int, default=0, help="--arch: number of layers (0: as many as --model has)")
+    ap.add_argument("--arch-prefill", default="512,2048", help="--arch: prompt lengths, comma separated")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.arch:
+        return bench_arch(args)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -4,8 +4,8 @@
 //   CTA tile 128 rows x 128 accumulator columns, K walked 64 elements (128 bytes, one 128B-swizzle row) per stage
 //   warp 0   TMA producer  A box [128 rows][128 B], B box [128 rows of W][128 B]  (GLU: 64 rows of gate + 64 rows of up)
 //   warp 1   MMA issuer    4 x tcgen05.mma.cta_group::1.kind::f16 (M128 N128 K16) per stage, tcgen05.commit frees the stage
-//   warps 2-5 epilogue     tcgen05.ld 32x32b.x32: thread = one row x 32 columns per load; store*scale | x += ls*acc |
-//                          silu(gate)*up, straight to global memory
+//   warps 2-5 epilogue     tcgen05.ld 32x32b.x32 (thread = one row x 32 columns), transposed through shared memory so that
+//                          a warp writes 128 contiguous bytes per row: store*scale | x += ls*acc | silu(gate)*up
 // The whole K range accumulates in TMEM (f32), so the accumulator is read once.  Ragged edges cost nothing extra: the
 // tensor maps carry the true extents, TMA fills rows >= T, weight rows >= O and the K tail with zeros, and the epilogue
 // masks its stores.  What the shape must satisfy: K and lda multiples of 8 elements (16-byte row pitch) and 16-byte
@@ -168,10 +168,13 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             }
             if (ok) tg_commit(tfull);
         }
-    } else {   // ---- epilogue: TMEM lane quadrant = warp % 4, thread = one row ----
+    } else {   // ---- epilogue: TMEM lane quadrant = warp % 4 ----
+        // tcgen05.ld hands a thread one ROW of the tile (32 consecutive columns per load).  Writing rows from there would
+        // touch 32 different cache lines per instruction, so each 32 x 32 block goes through shared memory (the operand
+        // ring is idle by now: every MMA that read it has completed) and leaves with lane = column: 128 contiguous bytes
+        // per row, loads of the residual batched eight rows ahead of their stores.
         const int quad = warp & 3;
-        const int row = quad * 32 + lane;
-        const int t = m0 + row;
+        float* stg = reinterpret_cast<float*>(tiles) + (size_t)(warp - 2) * 32 * 33;
         const bool ok = mbar_wait_bounded(tfull, 0, abort_flag);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
@@ -181,42 +184,41 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 tg_tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
                 if constexpr (GLU) tg_tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(64 + c0), u);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (t < p.T) {
-                    const int o0 = n0 + c0;
-                    if (EPI == EPI_STORE) {
-                        float* dst = p.e.out + (size_t)t * p.e.ldo + o0;
-                        if (o0 + 32 <= p.O && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]) * p.e.scale, __uint_as_float(v[j + 1]) * p.e.scale,
-                                                                                 __uint_as_float(v[j + 2]) * p.e.scale, __uint_as_float(v[j + 3]) * p.e.scale);
-                        } else {
+                for (int j = 0; j < 32; j++) {
+                    float val = __uint_as_float(v[j]);
+                    if constexpr (GLU) val = silu(val) * __uint_as_float(u[j]);
+                    stg[lane * 33 + j] = val;
+                }
+                __syncwarp();
+                const int o = n0 + c0 + lane;
+                const int t0 = m0 + quad * 32;
+                if (o < p.O) {
+                    if constexpr (EPI == EPI_STORE) {
+                        float* __restrict__ dst = p.e.out + (size_t)t0 * p.e.ldo + o;
+#pragma unroll 8
+                        for (int r = 0; r < 32; r++)
+                            if (t0 + r < p.T) dst[(size_t)r * p.e.ldo] = stg[r * 33 + lane] * p.e.scale;
+                    } else if constexpr (EPI == EPI_RESID) {
+                        float* __restrict__ dst = p.e.out + (size_t)t0 * p.e.ldo + o;
+                        const float lsv = p.e.ls[o];
+#pragma unroll 1
+                        for (int r0 = 0; r0 < 32; r0 += 8) {
+                            float x[8];
 #pragma unroll
-                            for (int j = 0; j < 32; j++)
-                                if (o0 + j < p.O) dst[j] = __uint_as_float(v[j]) * p.e.scale;
-                        }
-                    } else if (EPI == EPI_RESID) {
-                        float* dst = p.e.out + (size_t)t * p.e.ldo + o0;
-                        if (o0 + 32 <= p.O && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+                            for (int r = 0; r < 8; r++) x[r] = (t0 + r0 + r < p.T) ? dst[(size_t)(r0 + r) * p.e.ldo] : 0.0f;
 #pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                float4 x = *reinterpret_cast<float4*>(dst + j);
-                                x.x += p.e.ls[o0 + j] * __uint_as_float(v[j]); x.y += p.e.ls[o0 + j + 1] * __uint_as_float(v[j + 1]);
-                                x.z += p.e.ls[o0 + j + 2] * __uint_as_float(v[j + 2]); x.w += p.e.ls[o0 + j + 3] * __uint_as_float(v[j + 3]);
-                                *reinterpret_cast<float4*>(dst + j) = x;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j++)
-                                if (o0 + j < p.O) dst[j] += p.e.ls[o0 + j] * __uint_as_float(v[j]);
+                            for (int r = 0; r < 8; r++)
+                                if (t0 + r0 + r < p.T) dst[(size_t)(r0 + r) * p.e.ldo] = x[r] + lsv * stg[(r0 + r) * 33 + lane];
                         }
                     } else {
-                        __nv_bfloat16* dst = p.e.act + (size_t)t * p.e.lda + o0;
-#pragma unroll
-                        for (int j = 0; j < 32; j++)
-                            if (o0 + j < p.O) dst[j] = __float2bfloat16_rn(silu(__uint_as_float(v[j])) * __uint_as_float(u[GLU ? j : 0]));
+                        __nv_bfloat16* __restrict__ dst = p.e.act + (size_t)t0 * p.e.lda + o;
+#pragma unroll 8
+                        for (int r = 0; r < 32; r++)
+                            if (t0 + r < p.T) dst[(size_t)r * p.e.lda] = __float2bfloat16_rn(stg[r * 33 + lane]);
                     }
                 }
+                __syncwarp();
             }
         }
     }

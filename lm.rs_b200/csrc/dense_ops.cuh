@@ -137,6 +137,7 @@ template <typename AT, typename WT> struct GemvRowsParams {
     const float* x; const float* nw; float eps;   // NORM = true
     const WT* w; const WT* w2;   // [O][K]; w2: the "up" matrix of EPI_GLU
     int K, O;
+    int ksplit;               // 1: the warps of a CTA split K of one row pair (few rows), 0: a warp per row pair
     EpiParams<AT> e;
 };
 template <typename WT> struct Vec16;
@@ -206,7 +207,7 @@ DN_DEVINL void dot_rows(const WT* const (&w)[NR], const float* __restrict__ xs, 
 }
 template <typename AT, typename WT, int EPI, bool NORM>
 __global__ void __launch_bounds__(256) gemv_rows_kernel(const GemvRowsParams<AT, WT> p) {
-    extern __shared__ __align__(16) float gv_xs[];   // [K rounded up to 4] the input row as f32, then 33 reduction slots
+    extern __shared__ __align__(16) float gv_xs[];   // [K rounded up to 4] the input row as f32, then reduction slots
     float* red = gv_xs + ((p.K + 3) & ~3);
     if (NORM) {
         float ss = 0.0f;
@@ -220,6 +221,31 @@ __global__ void __launch_bounds__(256) gemv_rows_kernel(const GemvRowsParams<AT,
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const bool vec = p.K % Vec16<WT>::N == 0;   // every weight row then starts on a 16-byte boundary
+    if (p.ksplit) {
+        // few output rows (a down or output projection): a warp per row pair would leave most of the GPU idle, so the
+        // warps of a CTA share a row pair, each walking one slice of K; partial sums meet in shared memory
+        constexpr int N = Vec16<WT>::N;
+        const int pieces = p.K / N;                                // ksplit is only chosen when K % N == 0
+        const int per = (pieces + nw - 1) / nw;
+        const int k0 = min(pieces, warp * per) * N, k1 = min(pieces, (warp + 1) * per) * N;
+        float* part = red + 36;                                    // [2][nw]
+        for (int o = 2 * blockIdx.x; o < p.O; o += 2 * gridDim.x) {
+            const int o1 = o + 1 < p.O ? o + 1 : o;
+            const WT* const rows[2] = {p.w + (size_t)o * p.K + k0, p.w + (size_t)o1 * p.K + k0};
+            float r[2];
+            dot_rows<WT, 2>(rows, gv_xs + k0, k1 - k0, lane, true, r);
+            if (lane == 0) { part[warp] = r[0]; part[nw + warp] = r[1]; }
+            __syncthreads();
+            if (warp == 0 && lane < 2) {
+                float a = 0.0f;
+                for (int w = 0; w < nw; w++) a += part[lane * nw + w];
+                if (lane == 0) epi_apply<EPI, AT>(p.e, 0, o, a, 0.0f);
+                else if (o1 != o) epi_apply<EPI, AT>(p.e, 0, o1, a, 0.0f);
+            }
+            __syncthreads();
+        }
+        return;
+    }
     if (EPI == EPI_GLU) {
         for (int o = blockIdx.x * nw + warp; o < p.O; o += gridDim.x * nw) {
             const WT* const rows[2] = {p.w + (size_t)o * p.K, p.w2 + (size_t)o * p.K};
@@ -321,12 +347,32 @@ struct QkvPostParams {
     PosSrc ps;
 };
 __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostParams p) {
+    // grid (T, Y): the warps of the Y CTAs of a token share its tasks -- one per q head, one per k head, one per 128
+    // value elements, one for the gates
     const int t = blockIdx.x;
     const uint32_t pos = pos_of(p.ps) + (uint32_t)t;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const int wid = blockIdx.y * nw + (threadIdx.x >> 5), wtotal = gridDim.y * nw;
     const float* row = p.qkv + (size_t)t * p.ld;
-    const int n_qk = p.H + p.G;
-    for (int task = warp; task < n_qk; task += nw) {   // q heads, then k heads
+    const int n_qk = p.H + p.G, nv = p.G * p.dv, v_tasks = (nv + 127) / 128;
+    const float* vsrc = row + (size_t)n_qk * p.dk;
+    const int n_tasks = n_qk + v_tasks + (p.has_gate ? 1 : 0);
+    for (int task = wid; task < n_tasks; task += wtotal) {
+        if (task >= n_qk + v_tasks) {
+            for (int h = lane; h < p.H; h += 32) p.gate_out[(size_t)t * p.H + h] = 1.0f / (1.0f + expf(-vsrc[nv + h]));
+            continue;
+        }
+        if (task >= n_qk) {
+            const float lam = p.v_mode == V_MIX ? *p.lambda : 0.0f;
+            const int i1 = min(nv, (task - n_qk + 1) * 128);
+            for (int i = (task - n_qk) * 128 + lane; i < i1; i += 32) {
+                float v = vsrc[i];
+                if (p.v_mode == V_FIRST) p.v_first[(size_t)t * nv + i] = v;
+                else if (p.v_mode == V_MIX) v = (1.0f - lam) * v + lam * p.v_first[(size_t)t * nv + i];
+                p.vcache[(size_t)pos * nv + i] = v;
+            }
+            continue;
+        }
         const bool is_q = task < p.H;
         const float* src = row + (size_t)task * p.dk;  // k heads follow the q heads directly
         float* dst = is_q ? p.q_out + ((size_t)t * p.H + task) * p.dk : p.kcache + ((size_t)pos * p.G + (task - p.H)) * p.dk;
@@ -350,17 +396,6 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostParams p) {
             for (int d = lane; d < p.dk; d += 32) dst[d] = src[d];
         }
     }
-    const float* vsrc = row + (size_t)n_qk * p.dk;
-    const int nv = p.G * p.dv;
-    const float lam = p.v_mode == V_MIX ? *p.lambda : 0.0f;
-    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
-        float v = vsrc[i];
-        if (p.v_mode == V_FIRST) p.v_first[(size_t)t * nv + i] = v;
-        else if (p.v_mode == V_MIX) v = (1.0f - lam) * v + lam * p.v_first[(size_t)t * nv + i];
-        p.vcache[(size_t)pos * nv + i] = v;
-    }
-    if (p.has_gate)
-        for (int h = threadIdx.x; h < p.H; h += blockDim.x) p.gate_out[(size_t)t * p.H + h] = 1.0f / (1.0f + expf(-vsrc[nv + h]));
 }
 
 // ---- attention --------------------------------------------------------------------------------------------------------
@@ -433,16 +468,34 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_rows_kernel(const AttnRow
         for (int c = 0; c < NI; c++) acc[i][c] = 0.0f;
     }
     const size_t krow = (size_t)p.G * p.dk, vrow = (size_t)p.G * p.dv;
+    const bool vec4 = (p.dk & 3) == 0 && (p.dv & 3) == 0;
     for (int tile = split; tile < n_tiles; tile += p.nsplit) {
         const int j0 = tile * ATT_KT;
         __syncthreads();   // previous tile fully consumed (also orders the Qs fill before the first use)
-        for (int e = threadIdx.x; e < ATT_KT * d4; e += blockDim.x) {
-            const int j = e / d4, d = e - j * d4;
-            Ks[j * ks + d] = (j0 + j < n_keys && d < p.dk) ? p.kcache[(size_t)(j0 + j) * krow + (size_t)g * p.dk + d] : 0.0f;
-        }
-        for (int e = threadIdx.x; e < ATT_KT * DVP; e += blockDim.x) {
-            const int j = e / DVP, c = e - j * DVP;
-            Vs[e] = (j0 + j < n_keys && c < p.dv) ? p.vcache[(size_t)(j0 + j) * vrow + (size_t)g * p.dv + c] : 0.0f;
+        if (vec4) {   // head sizes in whole 16-byte pieces: every K and V row of this head starts on a 16-byte boundary
+            const int kq = d4 >> 2;
+            for (int e = threadIdx.x; e < ATT_KT * kq; e += blockDim.x) {
+                const int j = e / kq, d = (e - j * kq) << 2;
+                float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (j0 + j < n_keys) v = *reinterpret_cast<const float4*>(p.kcache + (size_t)(j0 + j) * krow + (size_t)g * p.dk + d);
+                *reinterpret_cast<float4*>(Ks + j * ks + d) = v;
+            }
+            constexpr int VQ = DVP >> 2;
+            for (int e = threadIdx.x; e < ATT_KT * VQ; e += blockDim.x) {
+                const int j = e / VQ, c = (e - j * VQ) << 2;
+                float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (j0 + j < n_keys && c < p.dv) v = *reinterpret_cast<const float4*>(p.vcache + (size_t)(j0 + j) * vrow + (size_t)g * p.dv + c);
+                *reinterpret_cast<float4*>(Vs + j * DVP + c) = v;
+            }
+        } else {
+            for (int e = threadIdx.x; e < ATT_KT * d4; e += blockDim.x) {
+                const int j = e / d4, d = e - j * d4;
+                Ks[j * ks + d] = (j0 + j < n_keys && d < p.dk) ? p.kcache[(size_t)(j0 + j) * krow + (size_t)g * p.dk + d] : 0.0f;
+            }
+            for (int e = threadIdx.x; e < ATT_KT * DVP; e += blockDim.x) {
+                const int j = e / DVP, c = e - j * DVP;
+                Vs[e] = (j0 + j < n_keys && c < p.dv) ? p.vcache[(size_t)(j0 + j) * vrow + (size_t)g * p.dv + c] : 0.0f;
+            }
         }
         __syncthreads();
         float s0[RW], s1[RW];

@@ -20,6 +20,7 @@
 
 #include <algorithm>
 #include <map>
+#include <set>
 #include <string>
 #include <vector>
 
@@ -122,8 +123,14 @@ template <typename AT, typename WT> class GenetarModel : public ArchModel {
     size_t chunk_rows = 2048;
     int use_tc = 1;   // tcgen05 GEMM for aligned bf16 shapes (0: always the CUDA-core kernel)
     DenseGemmCtx gemm_ctx;
+    struct GraphEntry { cudaGraphExec_t exec = nullptr; uint64_t kernels = 0; };
+    std::map<int, GraphEntry> graphs;   // decode step per position bucket
+    std::set<int> warmed;
+    const StepParams* graph_step = nullptr;
+    int use_graph = 1;
 
     ~GenetarModel() override {
+        drop_graphs();
         for (void* p : owned) cudaFree(p);
     }
     template <typename T> int dalloc(T** p, size_t n) {
@@ -334,6 +341,7 @@ template <typename AT, typename WT> class GenetarModel : public ArchModel {
 
     int ensure_scratch(size_t rows) {
         if (rows <= cap) return 0;
+        drop_graphs();   // captured launches point into the old scratch
         for (void* p : {(void*)x, (void*)qkv, (void*)q, (void*)gate, (void*)vfirst, (void*)part, (void*)h, (void*)att, (void*)act, (void*)hn, (void*)d_rows}) dfree(p);
         cap = 0;
         if (dalloc(&x, rows * width) || dalloc(&qkv, rows * max_qkv) || dalloc(&q, rows * max_q) || dalloc(&gate, rows * max_H) ||
@@ -379,11 +387,14 @@ template <typename AT, typename WT> class GenetarModel : public ArchModel {
         gemm_tiled_kernel<AT, WT, EPI><<<dim3((O + 63) / 64, (T + 63) / 64), 256, 0, st>>>(p);
         return check_launch("gemm_tiled_kernel");
     }
-    template <int EPI, bool NORM> int launch_gemv(cudaStream_t st, const GemvRowsParams<AT, WT>& p) {
-        const size_t smem = ((size_t)((p.K + 3) & ~3) + 40) * 4;
+    template <int EPI, bool NORM> int launch_gemv(cudaStream_t st, GemvRowsParams<AT, WT> p) {
+        const size_t smem = ((size_t)((p.K + 3) & ~3) + 36 + 2 * 8 + 4) * 4;
         if (optin(gemv_rows_kernel<AT, WT, EPI, NORM>, smem)) return 1;
         const int rows_per_cta = EPI == EPI_GLU ? 8 : 16;
         int grid = (p.O + rows_per_cta - 1) / rows_per_cta;
+        // few rows: the warps of a CTA split K instead (two row pairs per CTA)
+        p.ksplit = EPI != EPI_GLU && grid < 2 * sms && p.K % Vec16<WT>::N == 0 && p.K >= 1024;
+        if (p.ksplit) grid = (p.O + 3) / 4;
         grid = std::max(1, std::min(grid, sms * 4));
         gemv_rows_kernel<AT, WT, EPI, NORM><<<grid, 256, smem, st>>>(p);
         return check_launch("gemv_rows_kernel");
@@ -467,7 +478,8 @@ template <typename AT, typename WT> class GenetarModel : public ArchModel {
                 p.rot_dims = c.rot.dims; p.rot_cos = L.rot_cos; p.rot_sin = L.rot_sin;
                 p.v_mode = L.v_mode; p.v_first = vfirst; p.lambda = L.vmix; p.has_gate = c.rotary;
                 p.q_out = q; p.gate_out = gate; p.kcache = L.kcache; p.vcache = L.vcache; p.ps = ps;
-                qkv_post_kernel<<<T, 128, 0, st>>>(p);
+                const int tasks = c.H + c.G + (c.G * c.dv + 127) / 128 + 1;
+                qkv_post_kernel<<<dim3(T, T >= 64 ? 1 : std::min(16, (tasks + 3) / 4)), 128, 0, st>>>(p);
                 if (check_launch("qkv_post_kernel")) return 1;
             }
             if (attention(st, L, T, ps, pos_hint)) return 1;
@@ -497,11 +509,56 @@ template <typename AT, typename WT> class GenetarModel : public ArchModel {
         return matmul<EPI_STORE>(st, m, hn, width, head, nullptr, width, vocab, e);
     }
 
+    // A decode step has the same launches for every position of a bucket (the key-split count of the attention is the
+    // only thing that depends on the position, and it is constant over 64 positions, then fixed), and token and position
+    // are read on the device: the step is captured once per bucket into a CUDA graph and replayed.  The first step of a
+    // bucket runs uncaptured (it also raises the shared-memory limits of the kernels it meets).
     int decode_enqueue(cudaStream_t st, const StepParams* d_step, uint32_t pos_hint) override {
         if (pos_hint >= max_tokens) { error = "position beyond the cache (max_tokens)"; return 1; }
         PosSrc ps{d_step, 0};
-        if (run_layers(st, 1, ps, pos_hint)) return 1;
-        return head_rows(st, 1, nullptr, d_logits);
+        const int bucket = (int)std::min<uint32_t>(pos_hint / ATT_KT + 1, (uint32_t)MAX_SPLIT);
+        const uint32_t hint = bucket < MAX_SPLIT ? pos_hint : std::max<uint32_t>(pos_hint, (uint32_t)MAX_SPLIT * ATT_KT);
+        if (!use_graph || keep_layers || d_step != graph_step) {
+            if (d_step != graph_step) { drop_graphs(); graph_step = d_step; }
+            if (!use_graph || keep_layers) {
+                if (run_layers(st, 1, ps, hint)) return 1;
+                return head_rows(st, 1, nullptr, d_logits);
+            }
+        }
+        auto it = graphs.find(bucket);
+        if (it == graphs.end()) {
+            if (!warmed.count(bucket)) {
+                warmed.insert(bucket);
+                if (run_layers(st, 1, ps, hint)) return 1;
+                return head_rows(st, 1, nullptr, d_logits);
+            }
+            const uint64_t before = launches;
+            GCK(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+            int rc = run_layers(st, 1, ps, hint);
+            if (!rc) rc = head_rows(st, 1, nullptr, d_logits);
+            cudaGraph_t g = nullptr;
+            cudaError_t ce = cudaStreamEndCapture(st, &g);
+            if (rc || ce != cudaSuccess) {
+                if (g) cudaGraphDestroy(g);
+                if (!rc) error = std::string("cudaStreamEndCapture: ") + cudaGetErrorString(ce);
+                return 1;
+            }
+            GraphEntry ge;
+            ge.kernels = launches - before;
+            launches = before;
+            ce = cudaGraphInstantiate(&ge.exec, g, 0);
+            cudaGraphDestroy(g);
+            if (ce != cudaSuccess) { error = std::string("cudaGraphInstantiate: ") + cudaGetErrorString(ce); return 1; }
+            it = graphs.emplace(bucket, ge).first;
+        }
+        GCK(cudaGraphLaunch(it->second.exec, st));
+        launches += it->second.kernels;
+        return 0;
+    }
+    void drop_graphs() {
+        for (auto& kv : graphs) cudaGraphExecDestroy(kv.second.exec);
+        graphs.clear();
+        warmed.clear();
     }
 
     int forward_tokens(cudaStream_t st, const uint32_t* tokens, size_t n, uint32_t pos, const uint32_t* want, size_t n_want, float* d_out) override {
@@ -577,6 +634,7 @@ template <typename AT, typename WT> class GenetarModel : public ArchModel {
     void set_option(const char* name, int value) override {
         if (!strcmp(name, "chunk_rows")) chunk_rows = (size_t)std::max(1, value);
         else if (!strcmp(name, "tensor_cores")) use_tc = value;
+        else if (!strcmp(name, "graphs")) { use_graph = value; if (!value) drop_graphs(); }
     }
 };
 

@@ -210,6 +210,10 @@ def test_long_greedy_generation_through_the_generate_loop(gpu_lib, tmp_path, dty
     # forward_argmax is the same pick
     m.forward_tokens(prompt[:-1], 0, [])
     assert m.forward_argmax(prompt[-1], len(prompt) - 1) == ids[0]
+    # decode steps replayed from CUDA graphs and launched one by one are the same arithmetic
+    m.set_option("graphs", 0)
+    m.forward_tokens(prompt[:-1], 0, [])
+    assert m.generate_greedy(prompt[-1], len(prompt) - 1, n_new).tolist() == ids
     with pytest.raises(gpu_lib.LmrsError):
         m.forward(1, 21 + n_new)   # beyond the cache
     m.close()
