@@ -285,10 +285,14 @@ template <typename AT, typename WT> class GenetarModel : public ArchModel {
         if (need(st, "embed", {vocab, width}, &t) || dalloc(&embed, t->numel()) || upload_w(t, embed)) return 1;
         if (cfg.at("embedding").has("bigram")) {
             const Json& b = cfg.at("embedding").at("bigram");
-            buckets = (uint32_t)b.at("buckets").number(0);
-            mul_prev = (uint32_t)b.at("mul_prev").number(0);
-            mul_cur = (uint32_t)b.at("mul_cur").number(0);
-            if (buckets == 0) { error = "config.json: embedding.bigram.buckets must be positive"; return 1; }
+            const double nb = b.at("buckets").number(0);
+            if (!(nb >= 1.0 && nb < 2147483648.0)) { error = "config.json: embedding.bigram.buckets must be a positive 31-bit number"; return 1; }
+            buckets = (uint32_t)nb;
+            // (prev * a + cur * b) mod m only needs a and b modulo m: reduced here, the products on the device stay below 2^63
+            auto mod_m = [&](double v) { return (uint32_t)((unsigned long long)fabs(v) % buckets); };
+            if (b.at("mul_prev").number(0) < 0 || b.at("mul_cur").number(0) < 0) { error = "config.json: negative bigram multipliers are not supported"; return 1; }
+            mul_prev = mod_m(b.at("mul_prev").number(0));
+            mul_cur = mod_m(b.at("mul_cur").number(0));
             if (need(st, "bigram", {(int64_t)buckets + 1, width}, &t) || dalloc(&bigram, t->numel()) || upload_w(t, bigram)) return 1;
         }
         if (need(st, "head", {vocab, width}, &t) || dalloc(&head, t->numel()) || upload_w(t, head)) return 1;
@@ -315,7 +319,9 @@ template <typename AT, typename WT> class GenetarModel : public ArchModel {
                 else {
                     L.v_mode = V_MIX;
                     if (nv != layers[first_vmix].c.G * layers[first_vmix].c.dv) { error = "layers that mix values must have equally sized values"; return 1; }
-                    if (need(st, p + "mix.vmix", {}, &t) || upload_f32(t, &L.vmix)) return 1;
+                    t = st.find(p + "mix.vmix");
+                    if (!t || t->numel() != 1 || (t->dtype != "BF16" && t->dtype != "F32")) { error = "tensor '" + p + "mix.vmix' must hold one number"; return 1; }
+                    if (upload_f32(t, &L.vmix)) return 1;
                 }
             }
             if (c.has_mlp) {

@@ -1,7 +1,10 @@
 // generate.cpp -- minimal compiled-language caller of the C ABI (include/lmrs_b200.h): the greedy generate loop of the
 // reference's chat binary (src/bin/chat.rs:188-226 with --temperature 0) on token ids, without the tokenizer.
-//   usage: generate <model.lmrs> [n_new_tokens] [first_token ...]
-//   environment: LMRS_B200_GPUS=N    all N GPUs of this process behind one handle (lmrs_b200_create_multi)
+//   usage: generate <model.lmrs | model folder> [n_new_tokens] [first_token ...]
+//   A folder (config.json + model.safetensors, an architecture the library knows by name) is opened with lmrs_b200_open:
+//   the prompt goes through one forward_tokens pass, the rest through the same generate_greedy loop.
+//   environment: GENERATE_DTYPE=float32   operand format of a folder model (default bfloat16)
+//                LMRS_B200_GPUS=N    all N GPUs of this process behind one handle (lmrs_b200_create_multi)
 //                GENERATE_SERIAL=1   the reference's own call pattern: one forward() per prompt token, logits to the host,
 //                                    host argmax (chat.rs:196-214, sampler.rs:109-113)
 // Maps the model file like the reference does (memmap2, chat.rs:60-65) and hands it to lmrs_b200_create.  Default call
@@ -17,6 +20,7 @@
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
+#include <string>
 #include <vector>
 
 #include "lmrs_b200.h"
@@ -28,7 +32,7 @@ static int die(const char* what) {
 
 int main(int argc, char** argv) {
     if (argc < 2) {
-        std::fprintf(stderr, "usage: %s <model.lmrs> [n_new_tokens] [first_token ...]\n", argv[0]);
+        std::fprintf(stderr, "usage: %s <model.lmrs | model folder> [n_new_tokens] [first_token ...]\n", argv[0]);
         return 2;
     }
     const int n_new = argc > 2 ? std::atoi(argv[2]) : 16;
@@ -36,8 +40,31 @@ int main(int argc, char** argv) {
     for (int i = 3; i < argc; i++) prompt.push_back((uint32_t)std::strtoul(argv[i], nullptr, 10));
     if (prompt.empty()) prompt.push_back(1);
 
-    const int fd = open(argv[1], O_RDONLY);
     struct stat st;
+    if (stat(argv[1], &st) == 0 && S_ISDIR(st.st_mode)) {
+        // folder model: whole prompt but its last token in one pass, then the device-side greedy loop
+        const char* dt = std::getenv("GENERATE_DTYPE");
+        const int dtype = dt && std::string(dt) == "float32" ? 1 : 0;
+        lmrs_b200_t* fm = nullptr;
+        if (lmrs_b200_open(argv[1], -1, dtype, (uint32_t)(prompt.size() + (size_t)(n_new > 0 ? n_new : 0) + 1), &fm)) return die("open");
+        lmrs_args_t fa;
+        if (lmrs_b200_args(fm, &fa)) return die("args");
+        std::fprintf(stderr, "%s v%s: width %u, %u layers, vocab %u, %s\n", argv[1], lmrs_b200_version(), fa.dim, fa.n_layers, fa.vocab_size,
+                     dtype ? "float32" : "bfloat16");
+        for (uint32_t& t : prompt) t %= fa.vocab_size;
+        if (prompt.size() > 1 && lmrs_b200_forward_tokens(fm, prompt.data(), prompt.size() - 1, 0, nullptr, 0, nullptr)) return die("forward_tokens");
+        std::vector<uint32_t> out((size_t)(n_new > 0 ? n_new : 1));
+        uint32_t n_out = 0;
+        const auto tb = std::chrono::steady_clock::now();
+        if (lmrs_b200_generate_greedy(fm, prompt.back(), (uint32_t)prompt.size() - 1, (uint32_t)n_new, -1, out.data(), &n_out)) return die("generate_greedy");
+        const double sb = std::chrono::duration<double>(std::chrono::steady_clock::now() - tb).count();
+        for (uint32_t i = 0; i < n_out; i++) std::printf("%u ", out[i]);
+        std::printf("\n");
+        std::fprintf(stderr, "%u tokens in %.3f s: %.1f tok/s\n", n_out, sb, n_out / sb);
+        lmrs_b200_destroy(fm);
+        return 0;
+    }
+    const int fd = open(argv[1], O_RDONLY);
     if (fd < 0 || fstat(fd, &st) != 0) { std::perror(argv[1]); return 2; }
     void* map = mmap(nullptr, (size_t)st.st_size, PROT_READ, MAP_PRIVATE, fd, 0);
     if (map == MAP_FAILED) { std::perror("mmap"); return 2; }

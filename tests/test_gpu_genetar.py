@@ -257,3 +257,23 @@ def test_configuration_errors_are_reported(gpu_lib, tmp_path):
     with pytest.raises(gpu_lib.LmrsError):
         m.get_embeddings([1])
     m.close()
+
+
+def test_the_command_line_generates_from_a_folder(gpu_lib, tmp_path):
+    """lm.rs_b200/examples/generate on a model folder prints the ids that generate_greedy picks"""
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    subprocess.check_call(["make", "-C", os.path.join(root, "lm.rs_b200"), "-s", "examples"])
+    cfg = mixed_cfg()
+    W = G.random_weights(cfg, seed=11)
+    d = G.write_model(str(tmp_path / "cli"), cfg, W)
+    prompt = [3, 9, 27, 20]
+    env = dict(os.environ, GENERATE_DTYPE="float32")
+    r = subprocess.run([os.path.join(root, "lm.rs_b200", "examples", "generate"), d, "10"] + [str(t) for t in prompt],
+                       capture_output=True, text=True, env=env)
+    assert r.returncode == 0, r.stderr
+    m = gpu_lib.Transformer.open(d, dtype="float32", max_tokens=32)
+    m.forward_tokens(prompt[:-1], 0, [])
+    assert [int(x) for x in r.stdout.split()] == m.generate_greedy(prompt[-1], 3, 10).tolist()
+    m.close()
