@@ -1,7 +1,7 @@
 // dense_gemm.cuh -- many-row bf16 matrix products of the unquantized models on the 5th-generation tensor cores:
 //     out[T][O] (f32 accumulators) = A[T][K] (bf16) . W[O][K]^T (bf16),  then one of the epilogues of dense_ops.cuh
 // tcgen05.mma kind::f16 (bf16 x bf16 -> f32) with the accumulator in TMEM, operands staged by TMA:
-//   CTA tile 128 rows x 128 accumulator columns, K walked 64 elements (128 bytes, one 128B-swizzle row) per stage
+//   CTA tile 128 rows x 128 (or 64) accumulator columns, K walked 64 elements (128 bytes, one 128B-swizzle row) per stage
 //   warp 0   TMA producer  A box [128 rows][128 B], B box [128 rows of W][128 B]  (GLU: 64 rows of gate + 64 rows of up)
 //   warp 1   MMA issuer    4 x tcgen05.mma.cta_group::1.kind::f16 (M128 N128 K16) per stage, tcgen05.commit frees the stage
 //   warps 2-5 epilogue     tcgen05.ld 32x32b.x32 (thread = one row x 32 columns), transposed through shared memory so that
@@ -64,9 +64,9 @@ DN_DEVINL uint64_t tg_desc_sw128(const void* smem_tile) {
     d |= (uint64_t)2 << 61;
     return d;
 }
-// instruction descriptor: D = f32, A = B = bf16, both K-major, M = 128, N = 128, dense
-__host__ __device__ constexpr uint32_t tg_idesc() {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TG_N >> 3) << 17) | ((uint32_t)(TG_M >> 4) << 24);
+// instruction descriptor: D = f32, A = B = bf16, both K-major, M = 128, N = BN, dense
+template <int BN> __host__ __device__ constexpr uint32_t tg_idesc() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TG_M >> 4) << 24);
 }
 DN_DEVINL void tg_mma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -94,12 +94,16 @@ DN_DEVINL void tg_tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 
 // EPI_GLU: the B tile is 64 rows of the gate matrix followed by the same 64 rows of the up matrix, so accumulator
 // columns c and c + 64 belong to output column n0 + c and the CTA produces 64 output columns; otherwise 128.
-template <int EPI>
+// BN = accumulator columns per CTA: 128, or 64 for matrices with so few output rows that 128-wide tiles would leave
+// most SMs without a CTA (output and down projections at short prompts).
+template <int EPI, int BN>
 __global__ void __launch_bounds__(TG_THREADS, 2)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b2,
                     const TcGemmParams p) {
     constexpr bool GLU = EPI == EPI_GLU;
-    constexpr int OUT_COLS = GLU ? 64 : TG_N;
+    static_assert(BN == 128 || (BN == 64 && !GLU), "tile width");
+    constexpr int OUT_COLS = GLU ? 64 : BN;
+    constexpr uint32_t STAGE_TX = TG_A_BYTES + BN * TG_KB;   // bytes one stage receives (the ring keeps 32 KB slots)
     extern __shared__ uint8_t tg_raw[];
     uint8_t* sm = tg_raw + (((smem_u32(tg_raw) + 1023u) & ~1023u) - smem_u32(tg_raw));
     uint8_t* tiles = sm;
@@ -120,7 +124,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         fence_barrier_init();
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(TG_N) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -135,7 +139,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 const int s = g % TG_STAGES;
                 if (!mbar_wait_bounded(&empty[s], ((g / TG_STAGES) & 1) ^ 1, abort_flag)) break;
                 uint8_t* a_t = tiles + (size_t)s * TG_STAGE_BYTES;
-                mbar_expect_tx(&full[s], TG_STAGE_BYTES);
+                mbar_expect_tx(&full[s], STAGE_TX);
                 tg_tma_load_2d(a_t, &tm_a, g * TG_KB, m0, &full[s]);
                 if (GLU) {
                     tg_tma_load_2d(a_t + TG_A_BYTES, &tm_b, g * TG_KB, n0, &full[s]);
@@ -152,7 +156,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
     } else if (warp == 1) {
         if (lane == 0) {   // ---- MMA issuer ----
-            const uint32_t idesc = tg_idesc();
+            const uint32_t idesc = tg_idesc<BN>();
             bool ok = true;
             for (int g = 0; g < KS && ok; g++) {
                 const int s = g % TG_STAGES;
@@ -226,7 +230,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(TG_N) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(BN) : "memory");
     }
     if (threadIdx.x == 0 && *abort_flag && p.err) *p.err = 1;
 }
@@ -236,12 +240,13 @@ typedef CUresult (*TgEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_
                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 struct DenseGemmCtx {
+    int sms = 148;
     TgEncodeTiledFn enc = nullptr;
     bool tried = false;
     int* h_err = nullptr;   // mapped, pinned
     int* d_err = nullptr;
     std::map<std::pair<const void*, int>, CUtensorMap> wmaps;   // (weight matrix, box rows) -> tensor map
-    bool attr_set[3] = {false, false, false};
+    bool attr_set[3][2] = {};
     ~DenseGemmCtx() { if (h_err) cudaFreeHost(h_err); }
 };
 // a [rows][row_bytes used of pitch_bytes] byte matrix, box 128 bytes x box_rows rows, 128B swizzle, zeros outside
@@ -281,7 +286,9 @@ inline int dense_gemm_launch(DenseGemmCtx& c, cudaStream_t st, int T, const AT* 
         if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) || (w2 && (reinterpret_cast<uintptr_t>(w2) & 15))) return -1;
         if (*c.h_err) { err = "a tensor-core matrix product gave up waiting on one of its barriers (device status flag set)"; return 1; }
         constexpr bool GLU = EPI == EPI_GLU;
-        const int box_rows = GLU ? 64 : 128;
+        // 64-wide tiles when 128-wide ones would not give every SM a CTA
+        const bool narrow = !GLU && O > 64 && ((O + 127) / 128) * ((T + TG_M - 1) / TG_M) < c.sms;
+        const int box_rows = (GLU || narrow) ? 64 : 128;
         auto wmap = [&](const void* base, CUtensorMap* out) {
             auto key = std::make_pair(base, box_rows * 1000003 + O);
             auto it = c.wmaps.find(key);
@@ -298,17 +305,18 @@ inline int dense_gemm_launch(DenseGemmCtx& c, cudaStream_t st, int T, const AT* 
         if (!wmap(w, &tb)) return -1;
         tb2 = tb;
         if (GLU && !wmap(w2, &tb2)) return -1;
-        if (!c.attr_set[EPI]) {
-            if (cudaFuncSetAttribute(gemm_bf16_tc_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TG_SMEM) != cudaSuccess) {
-                err = "cudaFuncSetAttribute(gemm_bf16_tc_kernel) failed";
-                return 1;
-            }
-            c.attr_set[EPI] = true;
+        if (!c.attr_set[EPI][narrow]) {
+            cudaError_t ae = narrow ? cudaFuncSetAttribute(gemm_bf16_tc_kernel<EPI, GLU ? 128 : 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TG_SMEM)
+                                    : cudaFuncSetAttribute(gemm_bf16_tc_kernel<EPI, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TG_SMEM);
+            if (ae != cudaSuccess) { err = "cudaFuncSetAttribute(gemm_bf16_tc_kernel) failed"; return 1; }
+            c.attr_set[EPI][narrow] = true;
         }
         TcGemmParams p{};
         p.T = T; p.K = K; p.O = O; p.e = e; p.err = c.d_err;
-        const int out_cols = GLU ? 64 : TG_N;
-        gemm_bf16_tc_kernel<EPI><<<dim3((O + out_cols - 1) / out_cols, (T + TG_M - 1) / TG_M), TG_THREADS, TG_SMEM, st>>>(ta, tb, tb2, p);
+        const int out_cols = (GLU || narrow) ? 64 : TG_N;
+        const dim3 grid((O + out_cols - 1) / out_cols, (T + TG_M - 1) / TG_M);
+        if (narrow) gemm_bf16_tc_kernel<EPI, GLU ? 128 : 64><<<grid, TG_THREADS, TG_SMEM, st>>>(ta, tb, tb2, p);
+        else gemm_bf16_tc_kernel<EPI, 128><<<grid, TG_THREADS, TG_SMEM, st>>>(ta, tb, tb2, p);
         cudaError_t ce = cudaGetLastError();
         if (ce != cudaSuccess) { err = std::string("gemm_bf16_tc_kernel: ") + cudaGetErrorString(ce); return 1; }
         return 0;

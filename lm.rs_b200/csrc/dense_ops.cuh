@@ -416,23 +416,29 @@ template <typename AT> struct AttnRowsParams {
     AT* out;                  // [T][H*dv]
     float* part;              // nsplit > 1: [T][H][nsplit][dv + 2]
     int T, H, G, dk, dv, TQ, HC, nsplit;
+    int nbuf;                 // 2: K/V tiles double-buffered with cp.async (needs dk % 4 == 0 and dv % 4 == 0), 1: loaded in place
     float scale, softcap;
     PosSrc ps;
 };
+DN_DEVINL void cp_async16_zfill(void* smem_dst, const void* gsrc, bool valid) {   // 16 bytes, zeros when !valid
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
+}
 inline int attn_k_stride(int dk) { const int d4 = (dk + 3) & ~3; return d4 + ((4 - d4 % 32) + 32) % 32; }   // == 4 mod 32
-template <int RW, int NI> inline size_t attn_smem_bytes(int dk, int dv) {
+template <int RW, int NI> inline size_t attn_smem_bytes(int dk, int dv, int nbuf) {
     const int d4 = (dk + 3) & ~3, R = RW * ATT_WARPS;
-    return ((size_t)R * d4 + (size_t)ATT_KT * attn_k_stride(dk) + (size_t)ATT_KT * 32 * NI + (size_t)R * ATT_KT) * 4;
+    return ((size_t)R * d4 + (size_t)nbuf * ((size_t)ATT_KT * attn_k_stride(dk) + (size_t)ATT_KT * 32 * NI) + (size_t)R * ATT_KT) * 4;
 }
 template <typename AT, int RW, int NI>
 __global__ void __launch_bounds__(ATT_WARPS * 32) attn_rows_kernel(const AttnRowsParams<AT> p) {
     constexpr int R = RW * ATT_WARPS, DVP = 32 * NI;
     extern __shared__ float at_sm[];
     const int d4 = (p.dk + 3) & ~3, ks = d4 + ((4 - d4 % 32) + 32) % 32;
-    float* Qs = at_sm;                       // [R][d4]
-    float* Ks = Qs + (size_t)R * d4;         // [64][ks]
-    float* Vs = Ks + (size_t)ATT_KT * ks;    // [64][DVP]
-    float* Ps = Vs + (size_t)ATT_KT * DVP;   // [R][64]
+    float* Qs = at_sm;                                  // [R][d4]
+    float* Ks0 = Qs + (size_t)R * d4;                   // [nbuf][64][ks]
+    float* Vs0 = Ks0 + (size_t)p.nbuf * ATT_KT * ks;    // [nbuf][64][DVP]
+    float* Ps = Vs0 + (size_t)p.nbuf * ATT_KT * DVP;    // [R][64]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int kv_mul = p.H / p.G;
     const int chunks = (kv_mul + p.HC - 1) / p.HC;
@@ -469,8 +475,44 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_rows_kernel(const AttnRow
     }
     const size_t krow = (size_t)p.G * p.dk, vrow = (size_t)p.G * p.dv;
     const bool vec4 = (p.dk & 3) == 0 && (p.dv & 3) == 0;
+    const bool async = p.nbuf == 2;
+    // double-buffered form: the copies of tile i+1 are in flight (cp.async, no registers) while tile i is used
+    auto issue_tile = [&](int tile, int buf) {
+        const int j0 = tile * ATT_KT;
+        float* Kb = Ks0 + (size_t)buf * ATT_KT * ks;
+        float* Vb = Vs0 + (size_t)buf * ATT_KT * DVP;
+        const int kq = p.dk >> 2, vq = p.dv >> 2;
+        for (int e = threadIdx.x; e < ATT_KT * kq; e += blockDim.x) {
+            const int j = e / kq, d = (e - j * kq) << 2;
+            const bool ok = j0 + j < n_keys;
+            cp_async16_zfill(Kb + j * ks + d, ok ? p.kcache + (size_t)(j0 + j) * krow + (size_t)g * p.dk + d : p.kcache, ok);
+        }
+        for (int e = threadIdx.x; e < ATT_KT * vq; e += blockDim.x) {
+            const int j = e / vq, c = (e - j * vq) << 2;
+            const bool ok = j0 + j < n_keys;
+            cp_async16_zfill(Vb + j * DVP + c, ok ? p.vcache + (size_t)(j0 + j) * vrow + (size_t)g * p.dv + c : p.vcache, ok);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (async) {
+        if (p.dv < DVP)   // value columns beyond vdim are read by the p.V loop: zero them once in both buffers
+            for (int e = threadIdx.x; e < 2 * ATT_KT * (DVP - p.dv); e += blockDim.x) {
+                const int j = e / (DVP - p.dv), c = p.dv + (e - j * (DVP - p.dv));
+                Vs0[(size_t)j * DVP + c] = 0.0f;
+            }
+        if (split < n_tiles) issue_tile(split, 0);
+    }
+    int buf = 0;
     for (int tile = split; tile < n_tiles; tile += p.nsplit) {
         const int j0 = tile * ATT_KT;
+        float* Ks = Ks0 + (size_t)buf * ATT_KT * ks;
+        float* Vs = Vs0 + (size_t)buf * ATT_KT * DVP;
+        if (async) {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads();   // this tile has landed for everyone, and everyone is done with the other buffer
+            if (tile + p.nsplit < n_tiles) issue_tile(tile + p.nsplit, buf ^ 1);
+            buf ^= 1;
+        } else {
         __syncthreads();   // previous tile fully consumed (also orders the Qs fill before the first use)
         if (vec4) {   // head sizes in whole 16-byte pieces: every K and V row of this head starts on a 16-byte boundary
             const int kq = d4 >> 2;
@@ -498,6 +540,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_rows_kernel(const AttnRow
             }
         }
         __syncthreads();
+        }
         float s0[RW], s1[RW];
 #pragma unroll
         for (int i = 0; i < RW; i++) { s0[i] = 0.0f; s1[i] = 0.0f; }

@@ -271,6 +271,7 @@ template <typename AT, typename WT> class GenetarModel : public ArchModel {
 
     int load(const std::string& dir, const Json& cfg, const ArchOptions& opt) {
         sms = opt.sms;
+        gemm_ctx.sms = opt.sms;
         width = (int)cfg.at("width").number(0);
         vocab = (int)cfg.at("vocab").number(0);
         if (width <= 0 || vocab <= 0) { error = "config.json: width and vocab are required"; return 1; }
@@ -407,7 +408,9 @@ template <typename AT, typename WT> class GenetarModel : public ArchModel {
     }
 
     template <int RW, int NI> int launch_attn_t(cudaStream_t st, AttnRowsParams<AT> p, int grid_x, int grid_y) {
-        const size_t smem = attn_smem_bytes<RW, NI>(p.dk, p.dv);
+        // double-buffered K/V tiles when the head sizes allow 16-byte copies and two CTAs still fit an SM
+        p.nbuf = (p.dk % 4 == 0 && p.dv % 4 == 0 && attn_smem_bytes<RW, NI>(p.dk, p.dv, 2) <= 100 * 1024) ? 2 : 1;
+        const size_t smem = attn_smem_bytes<RW, NI>(p.dk, p.dv, p.nbuf);
         if (optin(attn_rows_kernel<AT, RW, NI>, smem)) return 1;
         attn_rows_kernel<AT, RW, NI><<<dim3(grid_x, grid_y, p.nsplit), ATT_WARPS * 32, smem, st>>>(p);
         return check_launch("attn_rows_kernel");
