@@ -17,8 +17,8 @@ def f32_to_bf16_bits(a: np.ndarray) -> np.ndarray:
     return ((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)).astype(np.uint16)
 
 
-def genetar_config(width, ff, n_layers, heads, kv_heads, head_dim, vocab, *, buckets=4099, rot_dims=None, eps=1e-6,
-                   softcap=30.0, logit_scale=1.0, pattern=("attention", "attention_2")):
+def genetar_config(width, ff, n_layers, heads, kv_heads, head_dim, vocab, *, buckets=4099, rot_dims=None, eps=1e-5,
+                   softcap=50.0, logit_scale=1.0, pattern=("attention", "attention_2")):
     """layers alternate through `pattern`; every layer mixes values and has a dense SiLU-GLU feed-forward"""
     layers = []
     for i in range(n_layers):
@@ -30,7 +30,7 @@ def genetar_config(width, ff, n_layers, heads, kv_heads, head_dim, vocab, *, buc
                         "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
         layers.append({"type": kind, "mixer": m, "mlp": {"kind": "dense", "ff": ff}})
     return {"architecture": "Genetar", "width": width, "vocab": vocab, "norm": {"eps": eps}, "logit_scale": logit_scale,
-            "embedding": {"bigram": {"buckets": buckets, "mul_prev": 31, "mul_cur": 17}}, "layers": layers}
+            "embedding": {"bigram": {"buckets": buckets, "mul_prev": 8191, "mul_cur": 127}}, "layers": layers}
 
 
 def genetar_tensors(cfg):
