@@ -84,7 +84,8 @@ int lmrs_b200_forward_tokens(lmrs_b200_t* m, const uint32_t* tokens, size_t n, u
 /* folder models: "keep_layers" 1 = keep the residual stream after every layer of each forward_tokens call (read it with
  * lmrs_b200_debug_buffer(m, "layers", ...): [n_layers][n][width]); "chunk_rows" = rows per internal pass of a long
  * portion; "tensor_cores" 0 = many-row products on the CUDA-core kernel even where the tcgen05 kernel applies; "graphs" 0 =
- * decode steps as plain launches instead of CUDA graph replays */
+ * decode steps as plain launches instead of CUDA graph replays; "pdl" 1 = decode kernels chained with programmatic
+ * dependent launch (measured slower, off by default) */
 int lmrs_b200_set_option(lmrs_b200_t* m, const char* name, int value);
 
 /* pub args: TransformerArgs (vocab_size, model_type, multimodal are the pub fields the bins read:

@@ -56,6 +56,13 @@ DN_DEVINL float block_sum(float v, float* red) {
     return r;
 }
 
+// Programmatic dependent launch: a kernel launched with the attribute may start while its predecessor in the stream is
+// still running; pdl_wait() blocks until the predecessor has completed and its writes are visible (a no-op without the
+// attribute), pdl_launch() lets the successor start its own pre-wait part now.  Every kernel here waits before it touches
+// anything but weights, so a chain of them stays ordered.
+DN_DEVINL void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+DN_DEVINL void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // position of row 0 of a step: a host constant, or read from the device-resident step parameters (decode graphs)
 struct PosSrc {
     const StepParams* sp;
@@ -75,6 +82,8 @@ template <typename WT> struct EmbedRowsParams {
     uint32_t buckets, mul_prev, mul_cur;
 };
 template <typename WT> __global__ void __launch_bounds__(128) embed_rows_kernel(const EmbedRowsParams<WT> p) {
+    pdl_launch();
+    pdl_wait();
     const uint32_t t = blockIdx.x, pos = pos_of(p.ps) + t;
     uint32_t tok;
     if (p.ps.sp) { tok = p.ps.sp->token; if (threadIdx.x == 0) p.tokens[pos] = tok; }
@@ -103,6 +112,8 @@ template <typename AT> struct NormRowsParams {
 };
 template <typename AT> __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const NormRowsParams<AT> p) {
     __shared__ float red[33];
+    pdl_launch();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* x = p.x + (size_t)(p.rows ? p.rows[r] : (uint32_t)r) * p.ldx;
     float ss = 0.0f;
@@ -138,6 +149,7 @@ template <typename AT, typename WT> struct GemvRowsParams {
     const WT* w; const WT* w2;   // [O][K]; w2: the "up" matrix of EPI_GLU
     int K, O;
     int ksplit;               // 1: the warps of a CTA split K of one row pair (few rows), 0: a warp per row pair
+    int pdl;                  // launched with programmatic dependent launch: prefetch weights before waiting for the input
     EpiParams<AT> e;
 };
 template <typename WT> struct Vec16;
@@ -209,6 +221,25 @@ template <typename AT, typename WT, int EPI, bool NORM>
 __global__ void __launch_bounds__(256) gemv_rows_kernel(const GemvRowsParams<AT, WT> p) {
     extern __shared__ __align__(16) float gv_xs[];   // [K rounded up to 4] the input row as f32, then reduction slots
     float* red = gv_xs + ((p.K + 3) & ~3);
+    pdl_launch();
+    if (p.pdl) {   // weights do not depend on the predecessor: ask L2 for this warp's first rows while waiting for it
+        const int w0 = (int)(blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5));
+        const int o = p.ksplit ? 2 * (int)blockIdx.x : (EPI == EPI_GLU ? w0 : 2 * w0);
+        if (o < p.O) {
+            const char* base = reinterpret_cast<const char*>(p.w + (size_t)o * p.K);
+            const size_t bytes = (size_t)p.K * sizeof(WT) * (EPI == EPI_GLU ? 1 : (o + 1 < p.O ? 2 : 1));
+            const size_t lo = p.ksplit ? bytes * (threadIdx.x >> 5) / (blockDim.x >> 5) : 0;
+            const size_t hi = p.ksplit ? bytes * ((threadIdx.x >> 5) + 1) / (blockDim.x >> 5) : bytes;
+            for (size_t b = lo + (size_t)(threadIdx.x & 31) * 128; b < hi && b < lo + 8192; b += 32 * 128)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(base + b));
+            if (EPI == EPI_GLU) {
+                const char* base2 = reinterpret_cast<const char*>(p.w2 + (size_t)o * p.K);
+                for (size_t b = (size_t)(threadIdx.x & 31) * 128; b < bytes && b < 8192; b += 32 * 128)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(base2 + b));
+            }
+        }
+    }
+    pdl_wait();
     if (NORM) {
         float ss = 0.0f;
         for (int c = threadIdx.x; c < p.K; c += blockDim.x) { const float v = p.x[c]; ss += v * v; }
@@ -280,6 +311,8 @@ template <typename AT, typename WT, int EPI>
 __global__ void __launch_bounds__(256) gemm_tiled_kernel(const GemmTiledParams<AT, WT> p) {
     constexpr int BM = 64, BN = 64, BK = 16;
     constexpr bool GLU = EPI == EPI_GLU;
+    pdl_launch();
+    pdl_wait();
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     __shared__ float W2s[GLU ? BK : 1][BN + 4];
@@ -349,6 +382,8 @@ struct QkvPostParams {
 __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostParams p) {
     // grid (T, Y): the warps of the Y CTAs of a token share its tasks -- one per q head, one per k head, one per 128
     // value elements, one for the gates
+    pdl_launch();
+    pdl_wait();
     const int t = blockIdx.x;
     const uint32_t pos = pos_of(p.ps) + (uint32_t)t;
     const int lane = threadIdx.x & 31, nw = blockDim.x >> 5;
@@ -433,6 +468,8 @@ template <int RW, int NI> inline size_t attn_smem_bytes(int dk, int dv, int nbuf
 template <typename AT, int RW, int NI>
 __global__ void __launch_bounds__(ATT_WARPS * 32) attn_rows_kernel(const AttnRowsParams<AT> p) {
     constexpr int R = RW * ATT_WARPS, DVP = 32 * NI;
+    pdl_launch();
+    pdl_wait();
     extern __shared__ float at_sm[];
     const int d4 = (p.dk + 3) & ~3, ks = d4 + ((4 - d4 % 32) + 32) % 32;
     float* Qs = at_sm;                                  // [R][d4]
@@ -621,6 +658,8 @@ template <typename AT> struct AttnCombineParams {
     int rows, H, dv, nsplit;   // rows = T * H
 };
 template <typename AT> __global__ void __launch_bounds__(128) attn_combine_kernel(const AttnCombineParams<AT> p) {
+    pdl_launch();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (r >= p.rows) return;

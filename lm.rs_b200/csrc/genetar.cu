@@ -127,7 +127,9 @@ template <typename AT, typename WT> class GenetarModel : public ArchModel {
     std::map<int, GraphEntry> graphs;   // decode step per position bucket
     std::set<int> warmed;
     const StepParams* graph_step = nullptr;
-    int use_graph = 1;
+    // programmatic dependent launch of the decode chain is an option, off by default: measured slower here (1.32 vs 1.14 ms
+    // per step at 16 layers of width 2048): the early-launched CTAs of the next kernels sit on the SMs while they wait
+    int use_graph = 1, use_pdl = 0;
 
     ~GenetarModel() override {
         drop_graphs();
@@ -367,6 +369,22 @@ template <typename AT, typename WT> class GenetarModel : public ArchModel {
         if (e != cudaSuccess) { error = std::string(what) + ": " + cudaGetErrorString(e); return 1; }
         return 0;
     }
+    // every kernel launch of the model; `pdl`: with the programmatic-dependent-launch attribute (decode chain)
+    template <typename... KArgs, typename... Args>
+    int launch_k(const char* what, cudaStream_t st, bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl ? 1 : 0;
+        launches++;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args...);
+        if (e != cudaSuccess) { error = std::string(what) + ": " + cudaGetErrorString(e); return 1; }
+        return 0;
+    }
+    bool pdl_now = false;   // set while a decode step is being enqueued
     template <typename K> int optin(K kernel, size_t smem) {
         if (smem <= 48 * 1024) return 0;
         static std::map<const void*, size_t> done;
@@ -402,9 +420,9 @@ template <typename AT, typename WT> class GenetarModel : public ArchModel {
         // few rows: the warps of a CTA split K instead (two row pairs per CTA)
         p.ksplit = EPI != EPI_GLU && grid < 2 * sms && p.K % Vec16<WT>::N == 0 && p.K >= 1024;
         if (p.ksplit) grid = (p.O + 3) / 4;
+        p.pdl = pdl_now ? 1 : 0;
         grid = std::max(1, std::min(grid, sms * 4));
-        gemv_rows_kernel<AT, WT, EPI, NORM><<<grid, 256, smem, st>>>(p);
-        return check_launch("gemv_rows_kernel");
+        return launch_k("gemv_rows_kernel", st, pdl_now, gemv_rows_kernel<AT, WT, EPI, NORM>, dim3(grid), dim3(256), smem, p);
     }
 
     template <int RW, int NI> int launch_attn_t(cudaStream_t st, AttnRowsParams<AT> p, int grid_x, int grid_y) {
@@ -412,8 +430,7 @@ template <typename AT, typename WT> class GenetarModel : public ArchModel {
         p.nbuf = (p.dk % 4 == 0 && p.dv % 4 == 0 && attn_smem_bytes<RW, NI>(p.dk, p.dv, 2) <= 100 * 1024) ? 2 : 1;
         const size_t smem = attn_smem_bytes<RW, NI>(p.dk, p.dv, p.nbuf);
         if (optin(attn_rows_kernel<AT, RW, NI>, smem)) return 1;
-        attn_rows_kernel<AT, RW, NI><<<dim3(grid_x, grid_y, p.nsplit), ATT_WARPS * 32, smem, st>>>(p);
-        return check_launch("attn_rows_kernel");
+        return launch_k("attn_rows_kernel", st, pdl_now, attn_rows_kernel<AT, RW, NI>, dim3(grid_x, grid_y, p.nsplit), dim3(ATT_WARPS * 32), smem, p);
     }
     template <int RW> int launch_attn_rw(cudaStream_t st, const AttnRowsParams<AT>& p, int gx, int gy) {
         const int ni = (p.dv + 31) / 32;
@@ -444,8 +461,7 @@ template <typename AT, typename WT> class GenetarModel : public ArchModel {
         if (p.nsplit > 1) {
             AttnCombineParams<AT> cp{};
             cp.part = part; cp.gate = p.gate; cp.out = att; cp.rows = T * c.H; cp.H = c.H; cp.dv = c.dv; cp.nsplit = p.nsplit;
-            attn_combine_kernel<AT><<<(cp.rows + 3) / 4, 128, 0, st>>>(cp);
-            return check_launch("attn_combine_kernel");
+            return launch_k("attn_combine_kernel", st, pdl_now, attn_combine_kernel<AT>, dim3((cp.rows + 3) / 4), dim3(128), 0, cp);
         }
         return 0;
     }
@@ -488,8 +504,8 @@ template <typename AT, typename WT> class GenetarModel : public ArchModel {
                 p.v_mode = L.v_mode; p.v_first = vfirst; p.lambda = L.vmix; p.has_gate = c.rotary;
                 p.q_out = q; p.gate_out = gate; p.kcache = L.kcache; p.vcache = L.vcache; p.ps = ps;
                 const int tasks = c.H + c.G + (c.G * c.dv + 127) / 128 + 1;
-                qkv_post_kernel<<<dim3(T, T >= 64 ? 1 : std::min(16, (tasks + 3) / 4)), 128, 0, st>>>(p);
-                if (check_launch("qkv_post_kernel")) return 1;
+                const dim3 grid(T, T >= 64 ? std::min(4, (tasks + 3) / 4) : std::min(16, (tasks + 3) / 4));
+                if (launch_k("qkv_post_kernel", st, pdl_now, qkv_post_kernel, grid, dim3(128), 0, p)) return 1;
             }
             if (attention(st, L, T, ps, pos_hint)) return 1;
             EpiParams<AT> e_res{}; e_res.out = x; e_res.ldo = width; e_res.ls = L.ls1;
@@ -523,6 +539,12 @@ template <typename AT, typename WT> class GenetarModel : public ArchModel {
     // are read on the device: the step is captured once per bucket into a CUDA graph and replayed.  The first step of a
     // bucket runs uncaptured (it also raises the shared-memory limits of the kernels it meets).
     int decode_enqueue(cudaStream_t st, const StepParams* d_step, uint32_t pos_hint) override {
+        pdl_now = use_pdl != 0;   // the embedding kernel opens the step as an ordinary launch, the rest chain on it
+        const int rc = decode_enqueue_impl(st, d_step, pos_hint);
+        pdl_now = false;
+        return rc;
+    }
+    int decode_enqueue_impl(cudaStream_t st, const StepParams* d_step, uint32_t pos_hint) {
         if (pos_hint >= max_tokens) { error = "position beyond the cache (max_tokens)"; return 1; }
         PosSrc ps{d_step, 0};
         const int bucket = (int)std::min<uint32_t>(pos_hint / ATT_KT + 1, (uint32_t)MAX_SPLIT);
@@ -644,6 +666,7 @@ template <typename AT, typename WT> class GenetarModel : public ArchModel {
         if (!strcmp(name, "chunk_rows")) chunk_rows = (size_t)std::max(1, value);
         else if (!strcmp(name, "tensor_cores")) use_tc = value;
         else if (!strcmp(name, "graphs")) { use_graph = value; if (!value) drop_graphs(); }
+        else if (!strcmp(name, "pdl")) { use_pdl = value; drop_graphs(); }
     }
 };
 

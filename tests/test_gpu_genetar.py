@@ -214,6 +214,12 @@ def test_long_greedy_generation_through_the_generate_loop(gpu_lib, tmp_path, dty
     m.set_option("graphs", 0)
     m.forward_tokens(prompt[:-1], 0, [])
     assert m.generate_greedy(prompt[-1], len(prompt) - 1, n_new).tolist() == ids
+    # ... and so are steps whose kernels are chained with programmatic dependent launch, replayed or not
+    for graphs in (1, 0):
+        m.set_option("graphs", graphs)
+        m.set_option("pdl", 1)
+        m.forward_tokens(prompt[:-1], 0, [])
+        assert m.generate_greedy(prompt[-1], len(prompt) - 1, n_new).tolist() == ids
     with pytest.raises(gpu_lib.LmrsError):
         m.forward(1, 21 + n_new)   # beyond the cache
     m.close()
