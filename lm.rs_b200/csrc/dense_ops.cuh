@@ -444,6 +444,13 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostParams p) {
 // depend on how the prompt was cut.  With nsplit > 1 (decode) CTA `split` walks tiles split, split + nsplit, ... and writes
 // (max, sum, unnormalised row) to scratch for attn_combine_kernel.
 constexpr int ATT_KT = 64, ATT_WARPS = 4;
+// exp and tanh of the attention inner loop on the special-function unit: ex2.approx is good to about 2e-7 relative, and
+// cap * (1 - 2 / (e^(2s/cap) + 1)) then carries an absolute error of about cap * 1e-7 -- the size of the f32 rounding of the
+// score itself (a relative error near zero does not matter: what enters the softmax is the score's absolute value)
+DN_DEVINL float att_exp(float x) { return __expf(x); }
+DN_DEVINL float att_softcap(float s, float cap, float inv_cap2) {   // inv_cap2 = 2 / cap
+    return cap * (1.0f - __fdividef(2.0f, __expf(s * inv_cap2) + 1.0f));
+}
 template <typename AT> struct AttnRowsParams {
     const float* q;           // [T][H*dk]
     const float* kcache; const float* vcache;
@@ -480,7 +487,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_rows_kernel(const AttnRow
     const int kv_mul = p.H / p.G;
     const int chunks = (kv_mul + p.HC - 1) / p.HC;
     const int g = blockIdx.y / chunks, h0 = (blockIdx.y % chunks) * p.HC;
-    const int t0 = blockIdx.x * p.TQ;
+    const int t0 = (int)(gridDim.x - 1 - blockIdx.x) * p.TQ;   // late query tiles see the most keys: they are scheduled first
     const int split = blockIdx.z;
     const uint32_t pos0 = pos_of(p.ps);
     // row slots
@@ -513,6 +520,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_rows_kernel(const AttnRow
     const size_t krow = (size_t)p.G * p.dk, vrow = (size_t)p.G * p.dv;
     const bool vec4 = (p.dk & 3) == 0 && (p.dv & 3) == 0;
     const bool async = p.nbuf == 2;
+    const float inv_cap2 = p.softcap > 0.0f ? 2.0f / p.softcap : 0.0f;
     // double-buffered form: the copies of tile i+1 are in flight (cp.async, no registers) while tile i is used
     auto issue_tile = [&](int tile, int buf) {
         const int j0 = tile * ATT_KT;
@@ -598,13 +606,13 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_rows_kernel(const AttnRow
         for (int i = 0; i < RW; i++) {
             const int last = (int)pos0 + r_t[i];   // last visible key of this row
             float a = s0[i] * p.scale, b = s1[i] * p.scale;
-            if (p.softcap > 0.0f) { a = p.softcap * tanhf(a / p.softcap); b = p.softcap * tanhf(b / p.softcap); }
+            if (p.softcap > 0.0f) { a = att_softcap(a, p.softcap, inv_cap2); b = att_softcap(b, p.softcap, inv_cap2); }
             const bool va = r_ok[i] && j0 + lane <= last, vb = r_ok[i] && j0 + lane + 32 <= last;
             a = va ? a : -1e30f; b = vb ? b : -1e30f;
             const float mt = warp_max(fmaxf(a, b));
             const float mn = fmaxf(m[i], mt);
-            const float pa = va ? expf(a - mn) : 0.0f, pb = vb ? expf(b - mn) : 0.0f;
-            corr[i] = expf(m[i] - mn);
+            const float pa = va ? att_exp(a - mn) : 0.0f, pb = vb ? att_exp(b - mn) : 0.0f;
+            corr[i] = att_exp(m[i] - mn);
             l[i] = l[i] * corr[i] + warp_sum(pa + pb);
             m[i] = mn;
             Ps[(size_t)(warp * RW + i) * ATT_KT + lane] = pa;
