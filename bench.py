@@ -246,7 +246,7 @@ def bench_arch(args):
     m.set_stream(stream.cuda_stream)
     ms, e2e_ms, launches = decode_legs(m, a.vocab_size)
     by = lf.decode_bytes_per_token(a, P + K // 2)
-    out["llama_q8"] = {"dtype": "int8 x int8 -> int32 groups, f32 accumulate, f32 KV cache", "weight_bytes": lf.decode_bytes_per_token(a),
+    out["lmrs_q8"] = {"dtype": "int8 x int8 -> int32 groups, f32 accumulate, f32 KV cache", "weight_bytes": lf.decode_bytes_per_token(a),
                        "prefill": pre, "decode": {"ms_per_step": ms, "tok_s": 1e3 / ms, "e2e_tok_s": 1e3 / e2e_ms, "launches_per_step": launches,
                                                   "algorithmic_bytes_per_step": by, "gb_s": by / ms / 1e6, "frac_of_hbm_peak": by / ms / 1e6 / peak_hbm}}
     gl += m.kernel_launches()
