@@ -283,3 +283,49 @@ def test_the_command_line_generates_from_a_folder(gpu_lib, tmp_path):
     m.forward_tokens(prompt[:-1], 0, [])
     assert [int(x) for x in r.stdout.split()] == m.generate_greedy(prompt[-1], 3, 10).tolist()
     m.close()
+
+
+def test_trace_replay_writes_the_logits_asked_for(gpu_lib, tmp_path):
+    """bin/trace_run: a prompt in portions, then single tokens, then a second request over the same cache"""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = mixed_cfg()
+    W = G.random_weights(cfg, seed=12)
+    d = G.write_model(str(tmp_path / "tr"), cfg, W)
+    a, b = tokens_for(cfg, 75, seed=5), tokens_for(cfg, 9, seed=6)
+    wa, _ = G.forward(cfg, W, a)
+    wb, _ = G.forward(cfg, W, b)
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": a[:66], "want": [0, 65]}], "end": []},
+             {"step": 1, "entries": [{"id": "x", "tokens": a[66:73], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "x", "tokens": a[73:74], "want": [0]}], "end": []},
+             {"step": 3, "entries": [{"id": "x", "tokens": a[74:75], "want": [0]}], "end": ["x"]},
+             {"step": 4, "entries": [{"id": "y", "tokens": b, "want": [8, 2]}], "end": ["y"]}]
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", d, "--dtype", "float32", "--out", str(out),
+                        "--max-tokens", "80"], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done %d" % i for i in range(5)]
+    assert not (out / "1.f32").exists()
+    V = cfg["vocab"]
+    for step, want in ((0, wa[[0, 65]]), (2, wa[[73]]), (3, wa[[74]]), (4, wb[[8, 2]])):
+        got = np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(-1, V)
+        assert G.rel_rms(got, want) < TOL["float32"], f"step {step}"
+
+
+def test_lmrs_files_open_by_path_and_take_token_steps(gpu_lib, lf, tmp_path):
+    """the path-based entry point serves the LMRS models too: forward_tokens on them is a run of decode steps"""
+    buf = lf.write_synthetic(lf.model_args("tiny-llama", 1))
+    path = tmp_path / "tiny.lmrs"
+    buf.tofile(path)
+    m = gpu_lib.Transformer.open(str(path))
+    ref, _ = gpu_lib.Transformer.new(buf)
+    toks = [3, 1, 4, 1, 5, 9]
+    got = m.forward_tokens(toks, 0, [5, 2])
+    rows = [ref.forward(t, i).copy() for i, t in enumerate(toks)]
+    assert np.array_equal(got[0], rows[5]) and np.array_equal(got[1], rows[2])
+    with pytest.raises(gpu_lib.LmrsError):
+        gpu_lib.Transformer.open(str(path), dtype="float32")
+    m.close(); ref.close()
