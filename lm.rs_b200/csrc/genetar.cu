@@ -222,6 +222,10 @@ template <typename AT, typename WT> class GenetarModel : public ArchModel {
         c.v_mix = m.has("v_mix") && m.at("v_mix").truth();
         if (c.H <= 0 || c.G <= 0 || c.dk <= 0 || c.dv <= 0 || c.H % c.G != 0) { error = where + ": bad head geometry"; return 1; }
         if (c.dv > 256) { error = where + ": vdim above 256 is not supported by the attention kernel"; return 1; }
+        if (attn_smem_bytes<4, 8>(c.dk, c.dv, 1) - (size_t)ATT_KT * 32 * 8 * 4 + (size_t)ATT_KT * 32 * ((c.dv + 31) / 32) * 4 > 227 * 1024) {
+            error = where + ": head dim " + std::to_string(c.dk) + " needs more shared memory than an SM has for the attention tiles";
+            return 1;
+        }
         if (c.rotary) {
             const Json& r = m.at("rot");
             if (!r.is_obj()) { error = where + ": attention_2 without 'rot'"; return 1; }
