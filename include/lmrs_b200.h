@@ -68,16 +68,20 @@ int lmrs_b200_create_multi(const uint8_t* file, size_t len, int n_gpus, lmrs_b20
  * lmrs_b200_open takes either an LMRS file (then it is lmrs_b200_create on the file's bytes) or a folder whose
  * config.json names its "architecture"; a registry inside the library maps that name to the model class ("Genetar": a
  * decoder of parallel attention + GLU blocks with unit-norm or partial-rotary attention, soft-capped scores, value
- * mixing across layers, per-head output gates and a hashed bigram input embedding).  The weights stay unquantized:
+ * mixing across layers, per-head output gates and a hashed bigram input embedding; "Tudatar": a decoder of sequential
+ * blocks with tanh norms around each sublayer, gated-delta-rule / latent-attention / windowed-attention mixers and
+ * routed-expert feed-forwards).  The weights stay unquantized:
  *   dtype 0  bfloat16 weights and matrix operands, f32 accumulation; residual, norms, scores, softmax, angles in f32
  *   dtype 1  float32 everywhere (no reduced-precision matrix mode)
  * max_tokens = positions the KV cache holds (0: 4096).  The returned handle works with forward / forward_argmax /
- * generate_greedy / forward_device / logits_device / read_kv / kernel_launches / args (model_type 3, q_type 0, dim = width,
+ * generate_greedy / forward_device / logits_device / read_kv / kernel_launches / args (model_type 3 Genetar, 4 Tudatar; q_type 0, dim = width,
  * seq_len = max_tokens) like any other; the entry points that take or return embeddings are LMRS-only. */
 int lmrs_b200_open(const char* path, int device, int dtype, uint32_t max_tokens, lmrs_b200_t** out);
 /* n tokens at positions pos .. pos+n-1 in ONE pass over the model (a whole prompt, or a portion of one continuing from
  * what earlier calls left in the cache); want[0..n_want) = indices into the n tokens whose logits are copied to
  * logits_out [n_want][vocab_size] (host).  Position 0 starts a new sequence: nothing of the previous one is read.
+ * A model with recurrent layers (their state is not addressed by position) continues where its last step ended or
+ * restarts at 0; any other position is an error.
  * LMRS-file handles run it as n decode steps. */
 int lmrs_b200_forward_tokens(lmrs_b200_t* m, const uint32_t* tokens, size_t n, uint32_t pos, const uint32_t* want,
                              size_t n_want, float* logits_out);

@@ -37,6 +37,9 @@ struct TcGemmParams {
     int T, K, O;
     EpiParams<__nv_bfloat16> e;
     int* err;   // mapped host word: set to 1 when a wait ran out
+    // grouped form (one matrix per expert over rows sorted by expert): blockIdx.z = group z owns rows grp[z] .. grp[z+1] of A and
+    // of the output and rows z*O .. z*O+O of the weight tensor map; null: one matrix for all T rows
+    const int* grp;
 };
 
 DN_DEVINL bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
@@ -114,7 +117,14 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * TG_M, n0 = blockIdx.x * OUT_COLS;
+    int m0 = blockIdx.y * TG_M, row_end = p.T, wrow0 = 0;
+    const int n0 = blockIdx.x * OUT_COLS;
+    if (p.grp) {   // tiles past the group's last row leave before anything is set up (the whole CTA takes this branch)
+        m0 += p.grp[blockIdx.z];
+        row_end = p.grp[blockIdx.z + 1];
+        wrow0 = (int)blockIdx.z * p.O;
+        if (m0 >= row_end) return;
+    }
     const int KS = (p.K * 2 + TG_KB - 1) / TG_KB;   // stages over K
 
     if (threadIdx.x == 0) {
@@ -142,10 +152,10 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 mbar_expect_tx(&full[s], STAGE_TX);
                 tg_tma_load_2d(a_t, &tm_a, g * TG_KB, m0, &full[s]);
                 if (GLU) {
-                    tg_tma_load_2d(a_t + TG_A_BYTES, &tm_b, g * TG_KB, n0, &full[s]);
-                    tg_tma_load_2d(a_t + TG_A_BYTES + 64 * TG_KB, &tm_b2, g * TG_KB, n0, &full[s]);
+                    tg_tma_load_2d(a_t + TG_A_BYTES, &tm_b, g * TG_KB, wrow0 + n0, &full[s]);
+                    tg_tma_load_2d(a_t + TG_A_BYTES + 64 * TG_KB, &tm_b2, g * TG_KB, wrow0 + n0, &full[s]);
                 } else {
-                    tg_tma_load_2d(a_t + TG_A_BYTES, &tm_b, g * TG_KB, n0, &full[s]);
+                    tg_tma_load_2d(a_t + TG_A_BYTES, &tm_b, g * TG_KB, wrow0 + n0, &full[s]);
                 }
                 issued = g + 1;
             }
@@ -200,26 +210,32 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 if (o < p.O) {
                     if constexpr (EPI == EPI_STORE) {
                         float* __restrict__ dst = p.e.out + (size_t)t0 * p.e.ldo + o;
+                        const float bias = p.e.bias ? p.e.bias[o] : 0.0f;
 #pragma unroll 8
                         for (int r = 0; r < 32; r++)
-                            if (t0 + r < p.T) dst[(size_t)r * p.e.ldo] = stg[r * 33 + lane] * p.e.scale;
+                            if (t0 + r < row_end) dst[(size_t)r * p.e.ldo] = p.e.bias ? stg[r * 33 + lane] * p.e.scale + bias : stg[r * 33 + lane] * p.e.scale;
                     } else if constexpr (EPI == EPI_RESID) {
                         float* __restrict__ dst = p.e.out + (size_t)t0 * p.e.ldo + o;
-                        const float lsv = p.e.ls[o];
+                        const float lsv = p.e.ls[o], lbv = p.e.lb ? p.e.lb[o] : 0.0f;
+                        const float alpha = p.e.tanh_alpha ? *p.e.tanh_alpha : 0.0f;
 #pragma unroll 1
                         for (int r0 = 0; r0 < 32; r0 += 8) {
                             float x[8];
 #pragma unroll
-                            for (int r = 0; r < 8; r++) x[r] = (t0 + r0 + r < p.T) ? dst[(size_t)(r0 + r) * p.e.ldo] : 0.0f;
+                            for (int r = 0; r < 8; r++) x[r] = (t0 + r0 + r < row_end) ? dst[(size_t)(r0 + r) * p.e.ldo] : 0.0f;
 #pragma unroll
                             for (int r = 0; r < 8; r++)
-                                if (t0 + r0 + r < p.T) dst[(size_t)(r0 + r) * p.e.ldo] = x[r] + lsv * stg[(r0 + r) * 33 + lane];
+                                if (t0 + r0 + r < row_end) {
+                                    float a = stg[(r0 + r) * 33 + lane];
+                                    if (p.e.tanh_alpha) a = tanhf(alpha * a);
+                                    dst[(size_t)(r0 + r) * p.e.ldo] = p.e.lb ? x[r] + (lsv * a + lbv) : x[r] + lsv * a;
+                                }
                         }
                     } else {
                         __nv_bfloat16* __restrict__ dst = p.e.act + (size_t)t0 * p.e.lda + o;
 #pragma unroll 8
                         for (int r = 0; r < 32; r++)
-                            if (t0 + r < p.T) dst[(size_t)r * p.e.lda] = __float2bfloat16_rn(stg[r * 33 + lane]);
+                            if (t0 + r < row_end) dst[(size_t)r * p.e.lda] = __float2bfloat16_rn(stg[r * 33 + lane]);
                     }
                 }
                 __syncwarp();
@@ -263,9 +279,11 @@ template <typename AT, typename WT> inline bool dense_gemm_usable(int T, int K, 
     return T >= 2 && K % 8 == 0 && lda % 8 == 0 && O >= 1;
 }
 // returns 0 on success, 1 on failure (message in err), -1 when the kernel cannot be used here (caller falls back)
+// n_groups > 0: the grouped form -- `w` (and `w2`) hold n_groups matrices [O][K] back to back, `grp` (device) the row offsets of the
+// groups in A and in the output, T the total number of rows and max_group_rows a bound on the rows of one group
 template <typename AT, typename WT, int EPI>
 inline int dense_gemm_launch(DenseGemmCtx& c, cudaStream_t st, int T, const AT* a, int lda, const WT* w, const WT* w2, int K, int O,
-                             const EpiParams<AT>& e, std::string& err) {
+                             const EpiParams<AT>& e, std::string& err, const int* grp = nullptr, int n_groups = 0, int max_group_rows = 0) {
     if constexpr (!std::is_same<AT, __nv_bfloat16>::value || !std::is_same<WT, __nv_bfloat16>::value) {
         return -1;
     } else {
@@ -287,14 +305,15 @@ inline int dense_gemm_launch(DenseGemmCtx& c, cudaStream_t st, int T, const AT* 
         if (*c.h_err) { err = "a tensor-core matrix product gave up waiting on one of its barriers (device status flag set)"; return 1; }
         constexpr bool GLU = EPI == EPI_GLU;
         // 64-wide tiles when 128-wide ones would not give every SM a CTA
+        const size_t w_rows = n_groups > 0 ? (size_t)n_groups * O : (size_t)O;
         const bool narrow = !GLU && O > 64 && ((O + 127) / 128) * ((T + TG_M - 1) / TG_M) < c.sms;
         const int box_rows = (GLU || narrow) ? 64 : 128;
         auto wmap = [&](const void* base, CUtensorMap* out) {
-            auto key = std::make_pair(base, box_rows * 1000003 + O);
+            auto key = std::make_pair(base, box_rows * 1000003 + (int)(w_rows % 1000003));
             auto it = c.wmaps.find(key);
             if (it == c.wmaps.end()) {
                 CUtensorMap m;
-                if (!tg_make_map(c, &m, base, (size_t)K * 2, (size_t)K * 2, (size_t)O, box_rows)) return false;
+                if (!tg_make_map(c, &m, base, (size_t)K * 2, (size_t)K * 2, w_rows, box_rows)) return false;
                 it = c.wmaps.emplace(key, m).first;
             }
             *out = it->second;
@@ -312,9 +331,10 @@ inline int dense_gemm_launch(DenseGemmCtx& c, cudaStream_t st, int T, const AT* 
             c.attr_set[EPI][narrow] = true;
         }
         TcGemmParams p{};
-        p.T = T; p.K = K; p.O = O; p.e = e; p.err = c.d_err;
+        p.T = T; p.K = K; p.O = O; p.e = e; p.err = c.d_err; p.grp = n_groups > 0 ? grp : nullptr;
         const int out_cols = (GLU || narrow) ? 64 : TG_N;
-        const dim3 grid((O + out_cols - 1) / out_cols, (T + TG_M - 1) / TG_M);
+        const int rows_y = n_groups > 0 ? std::min(T, max_group_rows) : T;
+        const dim3 grid((O + out_cols - 1) / out_cols, (rows_y + TG_M - 1) / TG_M, n_groups > 0 ? n_groups : 1);
         if (narrow) gemm_bf16_tc_kernel<EPI, GLU ? 128 : 64><<<grid, TG_THREADS, TG_SMEM, st>>>(ta, tb, tb2, p);
         else gemm_bf16_tc_kernel<EPI, 128><<<grid, TG_THREADS, TG_SMEM, st>>>(ta, tb, tb2, p);
         cudaError_t ce = cudaGetLastError();

@@ -3,13 +3,18 @@
 // architecture can use the same kernel:
 //   embed_rows_kernel        token embedding + optional hashed bigram embedding of (previous token, token)
 //   rmsnorm_rows_kernel      x / sqrt(mean(x^2) + eps) * w per row, optional row gather, output in the operand type
+//   tanhnorm_rows_kernel     tanh(alpha * x) * w + b per element (a norm without statistics), same gather and output
 //   gemv_rows_kernel         one token row:  weights streamed once (HBM-bound), optional fused RMS-norm prologue,
-//                            epilogues: store*scale | x += ls * acc | act(gate) * up
-//   gemm_tiled_kernel        many rows, any shape, CUDA cores (the f32 path and ragged shapes); same epilogues
+//                            epilogues: store*scale+bias | x += ls * f(acc) + lb | act(gate) * up | store in the operand
+//                            type; a batch dimension (per-head matrices, or experts picked by a device-side index list)
+//   gemm_tiled_kernel        many rows, any shape, CUDA cores (the f32 path and ragged shapes); same epilogues; batched
+//                            over column blocks (one matrix per head) or grouped over row ranges (one matrix per expert)
 //   qkv_post_kernel          per head: unit RMS norm of q/k or partial rotary, value mixing with an earlier layer's
 //                            values, sigmoid head gate, K/V rows written to the cache
-//   attn_rows_kernel         causal softmax attention with score scale and tanh soft-cap, grouped query heads, query
-//                            tile x KV head per CTA, optional split over the keys (decode) + attn_combine_kernel
+//   attn_rows_kernel         causal softmax attention with score scale and tanh soft-cap, optional sliding window and
+//                            logarithmic distance penalty, grouped query heads, query tile x KV head per CTA, K and V rows
+//                            with their own pitch (V may be a prefix of the K row: attention over a shared latent),
+//                            optional split over the keys (decode) + attn_combine_kernel
 // What the design wants in 32-bit (norms, scores, softmax, residual, angles) is 32-bit here in both operand types.
 #pragma once
 #include <cuda_bf16.h>
@@ -124,33 +129,68 @@ template <typename AT> __global__ void __launch_bounds__(256) rmsnorm_rows_kerne
     for (int c = threadIdx.x; c < p.n; c += blockDim.x) from_f(o[c], p.w ? x[c] * inv * p.w[c] : x[c] * inv);
 }
 
+// ---- norm without statistics: tanh(alpha * x) * w + b ------------------------------------------------------------------
+struct TanhNorm {          // the three tensors of one such norm; alpha is one float on the device
+    const float* alpha; const float* w; const float* b;
+};
+DN_DEVINL float tanhnorm_apply(const TanhNorm& n, float alpha, int c, float v) { return tanhf(alpha * v) * n.w[c] + n.b[c]; }
+template <typename AT> struct TanhNormRowsParams {
+    const float* x; int ldx;
+    const uint32_t* rows;   // optional gather
+    TanhNorm n;
+    AT* out; int ldo;
+    int width;
+};
+template <typename AT> __global__ void __launch_bounds__(256) tanhnorm_rows_kernel(const TanhNormRowsParams<AT> p) {
+    pdl_launch();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const float* x = p.x + (size_t)(p.rows ? p.rows[r] : (uint32_t)r) * p.ldx;
+    const float alpha = *p.n.alpha;
+    AT* o = p.out + (size_t)r * p.ldo;
+    for (int c = threadIdx.x; c < p.width; c += blockDim.x) from_f(o[c], tanhnorm_apply(p.n, alpha, c, x[c]));
+}
+
 // ---- epilogues shared by the matrix kernels ---------------------------------------------------------------------------
-enum { EPI_STORE = 0, EPI_RESID = 1, EPI_GLU = 2 };
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_GLU = 2, EPI_ACT = 3 };
 template <typename AT> struct EpiParams {
-    float* out; int ldo;      // EPI_STORE: out = acc * scale;  EPI_RESID: out += ls[o] * acc
+    float* out; int ldo;      // EPI_STORE: out = acc * scale (+ bias[o]);  EPI_RESID: out += ls[o] * f(acc) (+ lb[o])
     float scale;
     const float* ls;
-    AT* act; int lda;         // EPI_GLU: act = silu(gate) * up in the operand type
+    AT* act; int lda;         // EPI_GLU: act = silu(gate) * up in the operand type;  EPI_ACT: act = acc
+    const float* bias;        // EPI_STORE: optional bias of the projection
+    const float* tanh_alpha;  // EPI_RESID: when set, f(acc) = tanh(*tanh_alpha * acc) (a tanh norm on the way into the residual)
+    const float* lb;          // EPI_RESID: optional shift
 };
 DN_DEVINL float silu(float z) { return z / (1.0f + expf(-z)); }
 template <int EPI, typename AT> DN_DEVINL void epi_apply(const EpiParams<AT>& e, int t, int o, float a, float b) {
-    if (EPI == EPI_STORE) e.out[(size_t)t * e.ldo + o] = a * e.scale;
-    else if (EPI == EPI_RESID) e.out[(size_t)t * e.ldo + o] += e.ls[o] * a;
-    else from_f(e.act[(size_t)t * e.lda + o], silu(a) * b);
+    if (EPI == EPI_STORE) e.out[(size_t)t * e.ldo + o] = e.bias ? a * e.scale + e.bias[o] : a * e.scale;
+    else if (EPI == EPI_RESID) {
+        if (e.tanh_alpha) a = tanhf(*e.tanh_alpha * a);
+        e.out[(size_t)t * e.ldo + o] += e.lb ? e.ls[o] * a + e.lb[o] : e.ls[o] * a;
+    }
+    else if (EPI == EPI_GLU) from_f(e.act[(size_t)t * e.lda + o], silu(a) * b);
+    else from_f(e.act[(size_t)t * e.lda + o], a);
 }
 
 // ---- one row times a matrix: W [O][K] streamed once ----------------------------------------------------------------------
 // A warp owns output rows o = warp, warp + nwarps, ...; lanes walk K in 16-byte pieces, four pieces in flight per lane.
-// NORM: the input row is the f32 residual, normalised here (x * rsqrt(mean x^2 + eps) * nw) and rounded to the operand
-// type exactly as rmsnorm_rows_kernel does, so both routes feed the product the same numbers.
+// NORM: the input row is the f32 residual, normalised here and rounded to the operand type exactly as the row kernels
+// (rmsnorm_rows_kernel, tanhnorm_rows_kernel) do, so both routes feed the product the same numbers.
+//   NORM_RMS   x * rsqrt(mean x^2 + eps) * nw          NORM_TANH   tanh(alpha x) w + b
+// Batch (gridDim.y > 1): CTA row y multiplies input a + y * a_bs by matrix w + bidx[y] * w_bs (bidx null: y itself) and
+// writes at out/act + y * o_bs -- one matrix per head, or the experts a router picked, read from its device-side list.
+enum { NORM_NONE = 0, NORM_RMS = 1, NORM_TANH = 2 };
 template <typename AT, typename WT> struct GemvRowsParams {
-    const AT* a;              // [K] input row (NORM = false)
-    const float* x; const float* nw; float eps;   // NORM = true
+    const AT* a;              // [K] input row (NORM_NONE)
+    const float* x; const float* nw; float eps;   // NORM_RMS
+    TanhNorm tn;                                  // NORM_TANH
     const WT* w; const WT* w2;   // [O][K]; w2: the "up" matrix of EPI_GLU
     int K, O;
     int ksplit;               // 1: the warps of a CTA split K of one row pair (few rows), 0: a warp per row pair
     int pdl;                  // launched with programmatic dependent launch: prefetch weights before waiting for the input
     EpiParams<AT> e;
+    const int* bidx; long long a_bs, w_bs, o_bs;
 };
 template <typename WT> struct Vec16;
 template <> struct Vec16<float> { static constexpr int N = 4; };
@@ -217,11 +257,21 @@ DN_DEVINL void dot_rows(const WT* const (&w)[NR], const float* __restrict__ xs, 
 #pragma unroll
     for (int r = 0; r < NR; r++) out[r] = warp_sum(acc[r]);
 }
-template <typename AT, typename WT, int EPI, bool NORM>
-__global__ void __launch_bounds__(256) gemv_rows_kernel(const GemvRowsParams<AT, WT> p) {
+template <typename AT, typename WT, int EPI, int NORM>
+static __global__ void __launch_bounds__(256) gemv_rows_kernel(const GemvRowsParams<AT, WT> pp) {
     extern __shared__ __align__(16) float gv_xs[];   // [K rounded up to 4] the input row as f32, then reduction slots
+    GemvRowsParams<AT, WT> p = pp;
     float* red = gv_xs + ((p.K + 3) & ~3);
     pdl_launch();
+    if (gridDim.y > 1 || p.bidx) {   // the expert list is written by the step's router kernel: read it after the wait
+        if (p.bidx) pdl_wait();
+        const long long by = blockIdx.y, bw = p.bidx ? p.bidx[by] : by;
+        p.w += bw * p.w_bs;
+        if (p.w2) p.w2 += bw * p.w_bs;
+        if (p.a) p.a += by * p.a_bs;
+        if (p.e.out) p.e.out += by * p.o_bs;
+        if (p.e.act) p.e.act += by * p.o_bs;
+    }
     if (p.pdl) {   // weights do not depend on the predecessor: ask L2 for this warp's first rows while waiting for it
         const int w0 = (int)(blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5));
         const int o = p.ksplit ? 2 * (int)blockIdx.x : (EPI == EPI_GLU ? w0 : 2 * w0);
@@ -240,12 +290,15 @@ __global__ void __launch_bounds__(256) gemv_rows_kernel(const GemvRowsParams<AT,
         }
     }
     pdl_wait();
-    if (NORM) {
+    if (NORM == NORM_RMS) {
         float ss = 0.0f;
         for (int c = threadIdx.x; c < p.K; c += blockDim.x) { const float v = p.x[c]; ss += v * v; }
         ss = block_sum(ss, red);
         const float inv = 1.0f / sqrtf(ss / (float)p.K + p.eps);
         for (int c = threadIdx.x; c < p.K; c += blockDim.x) { AT r; from_f(r, p.x[c] * inv * p.nw[c]); gv_xs[c] = to_f(r); }
+    } else if (NORM == NORM_TANH) {
+        const float alpha = *p.tn.alpha;
+        for (int c = threadIdx.x; c < p.K; c += blockDim.x) { AT r; from_f(r, tanhnorm_apply(p.tn, alpha, c, p.x[c])); gv_xs[c] = to_f(r); }
     } else {
         for (int c = threadIdx.x; c < p.K; c += blockDim.x) gv_xs[c] = to_f(p.a[c]);
     }
@@ -301,14 +354,18 @@ __global__ void __launch_bounds__(256) gemv_rows_kernel(const GemvRowsParams<AT,
 // ---- many rows times a matrix on CUDA cores: out[T][O] = A[T][K] . W[O][K]^T, any shape --------------------------------
 // 64 x 64 output tile, K in steps of 16, 256 threads x (4 x 4) outputs; each output element adds its products in
 // ascending k, so a row's result does not depend on how many rows the call has.
+// blockIdx.z = batch entry z: matrix w + z * w_bs; without `grp` the input columns start at a + z * a_bs and the output
+// columns at out/act + z * o_bs (one matrix per head); with `grp` (device, [batches + 1] ascending row offsets) entry z owns
+// rows grp[z] .. grp[z+1] of the input and the output (one matrix per expert over rows sorted by expert).
 template <typename AT, typename WT> struct GemmTiledParams {
     const AT* a; int lda;
     const WT* w; const WT* w2;
     int T, K, O;
     EpiParams<AT> e;
+    const int* grp; long long a_bs, w_bs, o_bs;
 };
 template <typename AT, typename WT, int EPI>
-__global__ void __launch_bounds__(256) gemm_tiled_kernel(const GemmTiledParams<AT, WT> p) {
+static __global__ void __launch_bounds__(256) gemm_tiled_kernel(const GemmTiledParams<AT, WT> pp) {
     constexpr int BM = 64, BN = 64, BK = 16;
     constexpr bool GLU = EPI == EPI_GLU;
     pdl_launch();
@@ -316,7 +373,17 @@ __global__ void __launch_bounds__(256) gemm_tiled_kernel(const GemmTiledParams<A
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     __shared__ float W2s[GLU ? BK : 1][BN + 4];
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    GemmTiledParams<AT, WT> p = pp;
+    int row0 = 0;
+    if (gridDim.z > 1 || p.grp) {
+        const long long z = blockIdx.z;
+        p.w += z * p.w_bs;
+        if (p.w2) p.w2 += z * p.w_bs;
+        if (p.grp) { row0 = p.grp[z]; p.T = p.grp[z + 1]; }
+        else { p.a += z * p.a_bs; if (p.e.out) p.e.out += z * p.o_bs; if (p.e.act) p.e.act += z * p.o_bs; }
+    }
+    const int m0 = row0 + blockIdx.y * BM, n0 = blockIdx.x * BN;
+    if (m0 >= p.T) return;
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     float acc[4][4] = {}, acc2[GLU ? 4 : 1][4] = {};
     const int lr = threadIdx.x >> 2, lk = (threadIdx.x & 3) * 4;   // loader: row lr of the tile, k offset lk .. lk+3
@@ -379,7 +446,7 @@ struct QkvPostParams {
     float* kcache; float* vcache;                               // [max_tokens][G*dk], [max_tokens][G*dv]
     PosSrc ps;
 };
-__global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostParams p) {
+static __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostParams p) {
     // grid (T, Y): the warps of the Y CTAs of a token share its tasks -- one per q head, one per k head, one per 128
     // value elements, one for the gates
     pdl_launch();
@@ -434,8 +501,9 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostParams p) {
 }
 
 // ---- attention --------------------------------------------------------------------------------------------------------
-// score = (q . k) * scale, then softcap * tanh(score / softcap) when softcap > 0; row (t, head) sees keys 0 .. pos+t;
-// softmax in f32; output row times the head's gate (when given), written in the operand type as [T][H*dv].
+// score = (q . k) * scale, then softcap * tanh(score / softcap) when softcap > 0, then minus r1[head] * ln(1 + r2[head] *
+// distance) when r1 is given; row (t, head) at position i = pos+t sees keys j <= i, and only those with i - j < window when
+// window > 0 (key tiles wholly before the window are never loaded); softmax in f32; output row times the head's gate (when given), written in the operand type as [T][H*dv].
 // CTA = (tile of TQ query tokens, KV head, chunk of HC query heads of that KV head[, key split]); 4 warps x RW row slots,
 // row slot r = (token r / HC, head r % HC).  Keys are walked in tiles of 64 staged in shared memory: lane j scores keys j
 // and j + 32 of the tile for each of its rows (K rows padded so that the 16-byte reads of 32 lanes do not collide), an
@@ -458,6 +526,9 @@ template <typename AT> struct AttnRowsParams {
     AT* out;                  // [T][H*dv]
     float* part;              // nsplit > 1: [T][H][nsplit][dv + 2]
     int T, H, G, dk, dv, TQ, HC, nsplit;
+    int k_ld, v_ld;           // floats between consecutive positions of the K and of the V cache (>= G*dk, G*dv)
+    int window;               // > 0: sliding window of that many keys (the row's own included); 0: all earlier keys
+    const float* r1; const float* r2;   // [H] distance penalty r1 * ln(1 + r2 * (i - j)), or null
     int nbuf;                 // 2: K/V tiles double-buffered with cp.async (needs dk % 4 == 0 and dv % 4 == 0), 1: loaded in place
     float scale, softcap;
     PosSrc ps;
@@ -473,7 +544,7 @@ template <int RW, int NI> inline size_t attn_smem_bytes(int dk, int dv, int nbuf
     return ((size_t)R * d4 + (size_t)nbuf * ((size_t)ATT_KT * attn_k_stride(dk) + (size_t)ATT_KT * 32 * NI) + (size_t)R * ATT_KT) * 4;
 }
 template <typename AT, int RW, int NI>
-__global__ void __launch_bounds__(ATT_WARPS * 32) attn_rows_kernel(const AttnRowsParams<AT> p) {
+static __global__ void __launch_bounds__(ATT_WARPS * 32) attn_rows_kernel(const AttnRowsParams<AT> p) {
     constexpr int R = RW * ATT_WARPS, DVP = 32 * NI;
     pdl_launch();
     pdl_wait();
@@ -510,15 +581,20 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_rows_kernel(const AttnRow
     const int t_last = min(p.T, t0 + p.TQ) - 1;
     const int n_keys = (int)pos0 + t_last + 1;           // keys this CTA's last row sees
     const int n_tiles = (n_keys + ATT_KT - 1) / ATT_KT;
+    // the CTA's first row has the earliest window: tiles before its first visible key are skipped by every row
+    const int first_tile = p.window > 0 ? max(0, (int)pos0 + t0 - p.window + 1) / ATT_KT : 0;
     float m[RW], l[RW], acc[RW][NI];
+    float pen1[RW], pen2[RW];
+#pragma unroll
+    for (int i = 0; i < RW; i++) { pen1[i] = p.r1 && r_ok[i] ? p.r1[r_h[i]] : 0.0f; pen2[i] = p.r1 && r_ok[i] ? p.r2[r_h[i]] : 0.0f; }
 #pragma unroll
     for (int i = 0; i < RW; i++) {
         m[i] = -1e30f; l[i] = 0.0f;
 #pragma unroll
         for (int c = 0; c < NI; c++) acc[i][c] = 0.0f;
     }
-    const size_t krow = (size_t)p.G * p.dk, vrow = (size_t)p.G * p.dv;
-    const bool vec4 = (p.dk & 3) == 0 && (p.dv & 3) == 0;
+    const size_t krow = (size_t)p.k_ld, vrow = (size_t)p.v_ld;
+    const bool vec4 = (p.dk & 3) == 0 && (p.dv & 3) == 0 && (p.k_ld & 3) == 0 && (p.v_ld & 3) == 0;
     const bool async = p.nbuf == 2;
     const float inv_cap2 = p.softcap > 0.0f ? 2.0f / p.softcap : 0.0f;
     // double-buffered form: the copies of tile i+1 are in flight (cp.async, no registers) while tile i is used
@@ -545,10 +621,10 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_rows_kernel(const AttnRow
                 const int j = e / (DVP - p.dv), c = p.dv + (e - j * (DVP - p.dv));
                 Vs0[(size_t)j * DVP + c] = 0.0f;
             }
-        if (split < n_tiles) issue_tile(split, 0);
+        if (first_tile + split < n_tiles) issue_tile(first_tile + split, 0);
     }
     int buf = 0;
-    for (int tile = split; tile < n_tiles; tile += p.nsplit) {
+    for (int tile = first_tile + split; tile < n_tiles; tile += p.nsplit) {
         const int j0 = tile * ATT_KT;
         float* Ks = Ks0 + (size_t)buf * ATT_KT * ks;
         float* Vs = Vs0 + (size_t)buf * ATT_KT * DVP;
@@ -607,7 +683,13 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_rows_kernel(const AttnRow
             const int last = (int)pos0 + r_t[i];   // last visible key of this row
             float a = s0[i] * p.scale, b = s1[i] * p.scale;
             if (p.softcap > 0.0f) { a = att_softcap(a, p.softcap, inv_cap2); b = att_softcap(b, p.softcap, inv_cap2); }
-            const bool va = r_ok[i] && j0 + lane <= last, vb = r_ok[i] && j0 + lane + 32 <= last;
+            const int da = last - (j0 + lane), db = da - 32;   // distances of the two keys
+            if (p.r1) {
+                a -= pen1[i] * __logf(1.0f + pen2[i] * (float)max(da, 0));
+                b -= pen1[i] * __logf(1.0f + pen2[i] * (float)max(db, 0));
+            }
+            const bool va = r_ok[i] && da >= 0 && (p.window <= 0 || da < p.window);
+            const bool vb = r_ok[i] && db >= 0 && (p.window <= 0 || db < p.window);
             a = va ? a : -1e30f; b = vb ? b : -1e30f;
             const float mt = warp_max(fmaxf(a, b));
             const float mn = fmaxf(m[i], mt);
@@ -685,7 +767,7 @@ template <typename AT> __global__ void __launch_bounds__(128) attn_combine_kerne
 }
 
 // f32 <- bf16 widening of a weight tensor (the f32 operand mode keeps its weights as f32 in HBM)
-__global__ void widen_bf16_kernel(float* dst, const __nv_bfloat16* src, size_t n) {
+static __global__ void widen_bf16_kernel(float* dst, const __nv_bfloat16* src, size_t n) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) dst[i] = __bfloat162float(src[i]);
 }
 

@@ -1459,12 +1459,13 @@ extern "C" void lmrs_b200_destroy(lmrs_b200_t* m) {
 }
 
 // ---- models that come as a folder (config.json + model.safetensors): arch.h ----------------------------------------------
-namespace lmrs { void register_genetar(); }
+namespace lmrs { void register_genetar(); void register_tudatar(); }
 static void register_architectures() {
     static bool done = false;
     if (done) return;
     done = true;
     register_genetar();
+    register_tudatar();
 }
 static int open_arch(const char* dir, int device, int dtype, uint32_t max_tokens, lmrs_b200_t** out) {
     int ndev = 0;
@@ -1491,7 +1492,7 @@ static int open_arch(const char* dir, int device, int dtype, uint32_t max_tokens
     lmrs_args_t& a = m->args;
     a.dim = am->info.width; a.hidden_dim = am->info.ff; a.n_layers = am->info.n_layers; a.n_heads = am->info.heads;
     a.head_size = am->info.head_dim; a.n_kv_heads = am->info.kv_heads; a.vocab_size = am->info.vocab; a.seq_len = am->info.max_tokens;
-    a.rms_norm_eps = am->info.eps; a.rope_theta = 0.0f; a.q_type = 0; a.model_type = 3; a.group_size = 0; a.multimodal = 0;
+    a.rms_norm_eps = am->info.eps; a.rope_theta = 0.0f; a.q_type = 0; a.model_type = (uint8_t)am->info.model_type; a.group_size = 0; a.multimodal = 0;
     m->d_logits = am->d_logits;
     auto bail = [&](cudaError_t e, const char* what) {
         lmrs_b200_destroy(m);

@@ -1,0 +1,325 @@
+// mixer_ops.cuh -- what happens between a sequence mixer's input projection and its core, for the mixers that are not plain
+// multi-head attention, and the one core that is not attention (dense_ops.cuh has the attention kernel):
+//   latent_kv_post_kernel     attention through a shared latent: RMS norm of the query latent and of the key/value latent,
+//                             pairwise rotation of the shared rotated key part, latent + rotated part written to the cache
+//   latent_q_post_kernel      per query head: unrotated part to the operand type (it is multiplied into the latent space
+//                             next), rotated part rotated and placed behind the latent-space part of the query
+//   qkv_jointnorm_post_kernel q and k RMS-normalised over the WHOLE projection (all heads at once) with a weight, v divided
+//                             by its root mean square per head; k and v written to the cache
+//   delta_pre_kernel          gated delta rule: short causal convolution + SiLU on q, k, v channels (continued from a tail of
+//                             earlier inputs), unit-length q and k per head, write strength sigmoid
+//   conv_tail_update_kernel   the last taps-1 inputs of every channel become the tail for the next step
+//   delta_scan_kernel         S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q, token after token, the
+//                             state matrix of a head spread over the registers of the threads that own its columns
+//   gated_headnorm_kernel     o / rms(o) * w * sigmoid(gate) per head, in the operand type
+// Everything here is f32 (positions, angles, norms, decays, the recurrent state); only rows that feed the next matrix
+// product are written in the operand type.
+#pragma once
+#include "dense_ops.cuh"
+
+namespace lmrs {
+namespace dense {
+
+// first rot_dims entries of an n-vector rotated pairwise -- (2i, 2i+1) by the angle of cos[i], sin[i] -- the rest copied; one warp
+DN_DEVINL void rotate_pairs_warp(const float* src, float* dst, int n, int rot_dims, const float* c, const float* s, int lane) {
+    for (int i = lane; i < rot_dims / 2; i += 32) {
+        const float u = src[2 * i], v = src[2 * i + 1];
+        dst[2 * i] = u * c[i] - v * s[i];
+        dst[2 * i + 1] = v * c[i] + u * s[i];
+    }
+    for (int d = rot_dims + lane; d < n; d += 32) dst[d] = src[d];
+}
+
+// ---- attention through a latent: the projected row [query latent (rq) | key/value latent (rk) | rotated key part (dr)] ----
+template <typename AT> struct LatentKvPostParams {
+    const float* in; int ld;
+    int rq, rk, dr;
+    const float* wq; const float* wkv; float eps;                 // norm weights of the two latents
+    int rot_dims; const float* rot_cos; const float* rot_sin;      // [max_tokens][rot_dims/2], multiplier folded in
+    AT* cq_out;                                                   // [T][rq]
+    float* cache;                                                 // [max_tokens][rk + dr]
+    PosSrc ps;
+};
+template <typename AT> __global__ void __launch_bounds__(256) latent_kv_post_kernel(const LatentKvPostParams<AT> p) {
+    __shared__ float red[33];
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const uint32_t pos = pos_of(p.ps) + (uint32_t)t;
+    const float* row = p.in + (size_t)t * p.ld;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < p.rq; c += blockDim.x) ss += row[c] * row[c];
+    ss = block_sum(ss, red);
+    float inv = 1.0f / sqrtf(ss / (float)p.rq + p.eps);
+    for (int c = threadIdx.x; c < p.rq; c += blockDim.x) from_f(p.cq_out[(size_t)t * p.rq + c], row[c] * inv * p.wq[c]);
+    const float* kv = row + p.rq;
+    ss = 0.0f;
+    for (int c = threadIdx.x; c < p.rk; c += blockDim.x) ss += kv[c] * kv[c];
+    ss = block_sum(ss, red);
+    inv = 1.0f / sqrtf(ss / (float)p.rk + p.eps);
+    float* dst = p.cache + (size_t)pos * (p.rk + p.dr);
+    for (int c = threadIdx.x; c < p.rk; c += blockDim.x) dst[c] = kv[c] * inv * p.wkv[c];
+    if (threadIdx.x < 32) {
+        const int half = p.rot_dims / 2;
+        rotate_pairs_warp(kv + p.rk, dst + p.rk, p.dr, p.rot_dims, p.rot_cos + (size_t)pos * half, p.rot_sin + (size_t)pos * half, threadIdx.x);
+    }
+}
+
+template <typename AT> struct LatentQPostParams {
+    const float* q;           // [T][H * (dn + dr)], head by head [unrotated | rotated]
+    int H, dn, dr, rk;
+    int rot_dims; const float* rot_cos; const float* rot_sin;
+    AT* qn_out;               // [T][H * dn]
+    float* qabs;              // [T][H * (rk + dr)]: the rotated part goes to columns rk .. rk+dr of each head
+    PosSrc ps;
+};
+template <typename AT> __global__ void __launch_bounds__(128) latent_q_post_kernel(const LatentQPostParams<AT> p) {
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x, lane = threadIdx.x & 31;
+    const int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (h >= p.H) return;
+    const uint32_t pos = pos_of(p.ps) + (uint32_t)t;
+    const float* src = p.q + ((size_t)t * p.H + h) * (p.dn + p.dr);
+    AT* qn = p.qn_out + ((size_t)t * p.H + h) * p.dn;
+    for (int d = lane; d < p.dn; d += 32) from_f(qn[d], src[d]);
+    const int half = p.rot_dims / 2;
+    rotate_pairs_warp(src + p.dn, p.qabs + ((size_t)t * p.H + h) * (p.rk + p.dr) + p.rk, p.dr, p.rot_dims,
+                      p.rot_cos + (size_t)pos * half, p.rot_sin + (size_t)pos * half, lane);
+}
+
+// ---- q and k normalised over the whole projection, v per head --------------------------------------------------------------
+struct QkvJointNormParams {
+    const float* qkv; int ld;   // [q (H*dk) | k (G*dk) | v (G*dv)], biases already added
+    int H, G, dk, dv;
+    const float* wq; const float* wk; float eps;
+    float* q_out;               // [T][H*dk]
+    float* kcache; float* vcache;
+    PosSrc ps;
+};
+static __global__ void __launch_bounds__(256) qkv_jointnorm_post_kernel(const QkvJointNormParams p) {
+    __shared__ float red[33];
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const uint32_t pos = pos_of(p.ps) + (uint32_t)t;
+    const float* row = p.qkv + (size_t)t * p.ld;
+    const int nq = p.H * p.dk, nk = p.G * p.dk;
+    if (blockIdx.y < 2) {
+        const bool is_q = blockIdx.y == 0;
+        const float* src = is_q ? row : row + nq;
+        const int n = is_q ? nq : nk;
+        const float* w = is_q ? p.wq : p.wk;
+        float* dst = is_q ? p.q_out + (size_t)t * nq : p.kcache + (size_t)pos * nk;
+        float ss = 0.0f;
+        for (int c = threadIdx.x; c < n; c += blockDim.x) ss += src[c] * src[c];
+        ss = block_sum(ss, red);
+        const float inv = 1.0f / sqrtf(ss / (float)n + p.eps);
+        for (int c = threadIdx.x; c < n; c += blockDim.x) dst[c] = src[c] * inv * w[c];
+        return;
+    }
+    const int lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int g = threadIdx.x >> 5; g < p.G; g += nw) {
+        const float* src = row + nq + nk + (size_t)g * p.dv;
+        float* dst = p.vcache + ((size_t)pos * p.G + g) * p.dv;
+        float ss = 0.0f;
+        for (int d = lane; d < p.dv; d += 32) ss += src[d] * src[d];
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)p.dv + p.eps);
+        for (int d = lane; d < p.dv; d += 32) dst[d] = src[d] * inv;
+    }
+}
+
+// ---- gated delta rule -------------------------------------------------------------------------------------------------------------
+// The projected row is [q (G*dk) | k (G*dk) | v (H*dv) | write-strength logits (H) | decay latent (ra) | gate latent (rg)].
+// Its first C = 2*G*dk + H*dv entries are the convolution's channels, in the order of the tail [taps-1][C] and of the taps
+// [C][taps] (last tap = current token).  An input before the sequence's start is zero; one before this step's first row
+// comes from the tail.
+constexpr int CONV_MAX_TAPS = 16;
+DN_DEVINL float conv_input(const float* in, int ld, const float* tail, int C, int taps, int tq, int c, uint32_t pos0) {
+    if (tq >= 0) return in[(size_t)tq * ld + c];
+    if ((long long)pos0 + tq < 0) return 0.0f;
+    return tail[(size_t)(taps - 1 + tq) * C + c];
+}
+template <typename AT> struct DeltaPreParams {
+    const float* in; int ld;
+    int H, G, dk, dv, taps, ra, rg;
+    const float* wconv;       // [C][taps]
+    const float* tail;        // [taps-1][C]
+    float* qkv_out;           // [T][C]: q (unit length / sqrt(dk)), k (unit length), v
+    float* beta;              // [T][H]
+    AT* a_lat; AT* g_lat;     // [T][ra], [T][rg]: operands of the second halves of the two low-rank projections
+    PosSrc ps;
+};
+template <typename AT> __global__ void __launch_bounds__(128) delta_pre_kernel(const DeltaPreParams<AT> p) {
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const uint32_t pos0 = pos_of(p.ps);
+    const int lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const int wid = blockIdx.y * nw + (threadIdx.x >> 5), wtotal = gridDim.y * nw;
+    const int nqk = 2 * p.G, nv = p.H * p.dv, C = nqk * p.dk + nv, v_tasks = (nv + 127) / 128;
+    const float* row = p.in + (size_t)t * p.ld;
+    float* out = p.qkv_out + (size_t)t * C;
+    auto conv_silu = [&](int c) {
+        float a = 0.0f;
+        for (int j = 0; j < p.taps; j++) a = fmaf(p.wconv[(size_t)c * p.taps + j], conv_input(p.in, p.ld, p.tail, C, p.taps, t - (p.taps - 1 - j), c, pos0), a);
+        return silu(a);
+    };
+    for (int task = wid; task < nqk + v_tasks + 1; task += wtotal) {
+        if (task < nqk) {   // one q or k head: convolution, SiLU, unit length (q also / sqrt(dk))
+            const int c0 = task * p.dk;
+            float ss = 0.0f;
+            for (int d = lane; d < p.dk; d += 32) { const float v = conv_silu(c0 + d); out[c0 + d] = v; ss += v * v; }
+            ss = warp_sum(ss);
+            const float inv = (task < p.G ? 1.0f / sqrtf((float)p.dk) : 1.0f) / sqrtf(ss + 1e-6f);
+            for (int d = lane; d < p.dk; d += 32) out[c0 + d] *= inv;   // a lane rescales what it wrote itself
+        } else if (task < nqk + v_tasks) {
+            const int c0 = nqk * p.dk, i0 = (task - nqk) * 128, i1 = min(nv, i0 + 128);
+            for (int i = i0 + lane; i < i1; i += 32) out[c0 + i] = conv_silu(c0 + i);
+        } else {
+            for (int h = lane; h < p.H; h += 32) p.beta[(size_t)t * p.H + h] = 1.0f / (1.0f + expf(-row[C + h]));
+            for (int i = lane; i < p.ra; i += 32) from_f(p.a_lat[(size_t)t * p.ra + i], row[C + p.H + i]);
+            for (int i = lane; i < p.rg; i += 32) from_f(p.g_lat[(size_t)t * p.rg + i], row[C + p.H + p.ra + i]);
+        }
+    }
+}
+struct ConvTailParams {
+    const float* in; int ld;
+    float* tail; int C, taps, T;
+    PosSrc ps;
+};
+static __global__ void __launch_bounds__(256) conv_tail_update_kernel(const ConvTailParams p) {
+    pdl_launch();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= p.C) return;
+    const uint32_t pos0 = pos_of(p.ps);
+    float nv[CONV_MAX_TAPS];
+#pragma unroll
+    for (int r = 0; r < CONV_MAX_TAPS; r++)
+        if (r < p.taps - 1) nv[r] = conv_input(p.in, p.ld, p.tail, p.C, p.taps, p.T - (p.taps - 1) + r, c, pos0);
+#pragma unroll
+    for (int r = 0; r < CONV_MAX_TAPS; r++)
+        if (r < p.taps - 1) p.tail[(size_t)r * p.C + c] = nv[r];
+}
+
+// The scan.  CTA = (block of state columns, head); a column j of the head's state S [dk][dv] belongs to `lpc` adjacent lanes,
+// lane s of them holding rows s, s + lpc, ... (at most DELTA_NR each) in registers.  Columns never interact: S^T k and S^T q
+// are sums down a column, the rank-one update adds k_i u_j.  Tokens are staged DELTA_TB at a time in shared memory (q, k, the
+// decays computed from the projected logits, v, beta); then every token costs two passes over the registers and two
+// reductions across the lpc lanes.  The order of every sum is fixed, so a token's result does not depend on the portion it
+// arrives in.  The state is read at the start (zeros when the step starts at position 0) and written back at the end.
+constexpr int DELTA_NR = 16, DELTA_TB = 8, DELTA_THREADS = 128;
+struct DeltaScanParams {
+    const float* qkv; int ld;   // [T][C]: q at 0, k at G*dk, v at 2*G*dk
+    const float* araw;          // [T][H*dk]: decay logits (second low-rank projection + bias)
+    const float* a_log;         // [H]
+    const float* beta;          // [T][H]
+    float* state;               // [H][dk][dv]
+    float* out;                 // [T][H*dv]
+    int T, H, G, dk, dv, lpc;
+    PosSrc ps;
+};
+inline int delta_lanes_per_column(int dk) { int l = 1; while (l * DELTA_NR < dk) l *= 2; return l; }   // dk <= 32 * DELTA_NR
+inline size_t delta_scan_smem(int dk, int lpc) { return (size_t)DELTA_TB * (3 * dk + DELTA_THREADS / lpc + 1) * 4; }
+static __global__ void __launch_bounds__(DELTA_THREADS) delta_scan_kernel(const DeltaScanParams p) {
+    extern __shared__ float ds_sm[];
+    pdl_launch();
+    pdl_wait();
+    const int cols = DELTA_THREADS / p.lpc;
+    float* qs = ds_sm;                          // [TB][dk]
+    float* ks = qs + DELTA_TB * p.dk;
+    float* gs = ks + DELTA_TB * p.dk;
+    float* vs = gs + DELTA_TB * p.dk;           // [TB][cols]
+    float* bs = vs + DELTA_TB * cols;           // [TB]
+    const int h = blockIdx.y, g = h / (p.H / p.G);
+    const int s = threadIdx.x % p.lpc, jl = threadIdx.x / p.lpc, j = blockIdx.x * cols + jl;
+    const bool col_ok = j < p.dv;
+    const uint32_t pos0 = pos_of(p.ps);
+    float S[DELTA_NR];
+    float* sp = p.state + ((size_t)h * p.dk) * p.dv + j;
+#pragma unroll
+    for (int r = 0; r < DELTA_NR; r++) {
+        const int i = s + r * p.lpc;
+        S[r] = (pos0 > 0 && col_ok && i < p.dk) ? sp[(size_t)i * p.dv] : 0.0f;
+    }
+    const float rate = expf(p.a_log[h]);
+    const int vq = 2 * p.G * p.dk;
+    for (int t0 = 0; t0 < p.T; t0 += DELTA_TB) {
+        const int nt = min(DELTA_TB, p.T - t0);
+        __syncthreads();   // the previous block of tokens is consumed
+        for (int e = threadIdx.x; e < nt * p.dk; e += blockDim.x) {
+            const int tt = e / p.dk, i = e - tt * p.dk;
+            const float* row = p.qkv + (size_t)(t0 + tt) * p.ld;
+            qs[tt * p.dk + i] = row[g * p.dk + i];
+            ks[tt * p.dk + i] = row[(p.G + g) * p.dk + i];
+            const float a = p.araw[((size_t)(t0 + tt) * p.H + h) * p.dk + i];
+            const float sp_a = a > 20.0f ? a : log1pf(expf(a));
+            gs[tt * p.dk + i] = expf(-rate * sp_a);
+        }
+        for (int e = threadIdx.x; e < nt * cols; e += blockDim.x) {
+            const int tt = e / cols, c = e - tt * cols, jj = blockIdx.x * cols + c;
+            vs[e] = jj < p.dv ? p.qkv[(size_t)(t0 + tt) * p.ld + vq + h * p.dv + jj] : 0.0f;
+        }
+        if (threadIdx.x < nt) bs[threadIdx.x] = p.beta[(size_t)(t0 + threadIdx.x) * p.H + h];
+        __syncthreads();
+        for (int tt = 0; tt < nt; tt++) {
+            const float* kq = ks + tt * p.dk;
+            const float* qq = qs + tt * p.dk;
+            const float* gq = gs + tt * p.dk;
+            float r0 = 0.0f, r1 = 0.0f;
+#pragma unroll
+            for (int r = 0; r < DELTA_NR; r += 2) {
+                const int i0 = s + r * p.lpc, i1 = i0 + p.lpc;
+                if (i0 < p.dk) { S[r] *= gq[i0]; r0 = fmaf(S[r], kq[i0], r0); }
+                if (i1 < p.dk) { S[r + 1] *= gq[i1]; r1 = fmaf(S[r + 1], kq[i1], r1); }
+            }
+            float rsum = r0 + r1;
+            for (int o = p.lpc >> 1; o > 0; o >>= 1) rsum += __shfl_xor_sync(0xffffffffu, rsum, o);
+            const float u = bs[tt] * (vs[tt * cols + jl] - rsum);
+            float o0 = 0.0f, o1 = 0.0f;
+#pragma unroll
+            for (int r = 0; r < DELTA_NR; r += 2) {
+                const int i0 = s + r * p.lpc, i1 = i0 + p.lpc;
+                if (i0 < p.dk) { S[r] = fmaf(kq[i0], u, S[r]); o0 = fmaf(S[r], qq[i0], o0); }
+                if (i1 < p.dk) { S[r + 1] = fmaf(kq[i1], u, S[r + 1]); o1 = fmaf(S[r + 1], qq[i1], o1); }
+            }
+            float osum = o0 + o1;
+            for (int o = p.lpc >> 1; o > 0; o >>= 1) osum += __shfl_xor_sync(0xffffffffu, osum, o);
+            if (s == 0 && col_ok) p.out[(size_t)(t0 + tt) * p.H * p.dv + (size_t)h * p.dv + j] = osum;
+        }
+    }
+    if (col_ok) {
+#pragma unroll
+        for (int r = 0; r < DELTA_NR; r++) {
+            const int i = s + r * p.lpc;
+            if (i < p.dk) sp[(size_t)i * p.dv] = S[r];
+        }
+    }
+}
+
+// o / sqrt(mean(o^2) + eps) * w[c] * sigmoid(gate logit) per (token, head): one warp each
+template <typename AT> struct GatedHeadNormParams {
+    const float* o; const float* graw;   // [rows][dv] each, rows = T * H
+    const float* w; float eps;
+    AT* out;
+    int rows, dv;
+};
+template <typename AT> __global__ void __launch_bounds__(128) gated_headnorm_kernel(const GatedHeadNormParams<AT> p) {
+    pdl_launch();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= p.rows) return;
+    const float* o = p.o + (size_t)r * p.dv;
+    const float* gr = p.graw + (size_t)r * p.dv;
+    float ss = 0.0f;
+    for (int c = lane; c < p.dv; c += 32) ss += o[c] * o[c];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)p.dv + p.eps);
+    for (int c = lane; c < p.dv; c += 32) from_f(p.out[(size_t)r * p.dv + c], o[c] * inv * p.w[c] / (1.0f + expf(-gr[c])));
+}
+
+}  // namespace dense
+}  // namespace lmrs

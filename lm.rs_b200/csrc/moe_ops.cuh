@@ -1,0 +1,132 @@
+// moe_ops.cuh -- a feed-forward made of routed experts, around the matrix kernels of dense_ops.cuh / dense_gemm.cuh:
+//   moe_router_kernel    router logits in f32 (f32 router matrix), score = sigmoid(logit), the `top` experts with the largest
+//                        score + correction[e] are chosen, their weights are score / (sum of chosen scores + 1e-20) * scale
+//   moe_sort_kernel      (token, choice) pairs counted and sorted by expert: row offsets per expert, the slot of every pair,
+//                        the token of every slot
+//   moe_gather_kernel    the normalised rows copied into expert order (the grouped matrix kernels then see one contiguous row
+//                        range per expert)
+//   moe_combine_kernel   x += f(sum over the token's choices of weight * expert output), f = a tanh norm on the way into the
+//                        residual (or the identity)
+// A one-row step needs no sorting: the one-row matrix kernel takes the chosen experts from the router's device-side list.
+#pragma once
+#include "dense_ops.cuh"
+
+namespace lmrs {
+namespace dense {
+
+template <typename AT> struct MoeRouterParams {
+    const AT* h; int ld;          // [T][width] normalised input (operand type)
+    const float* router;          // [E][width]
+    const float* correction;      // [E], added for the choice only
+    int E, top, width;
+    float scale;
+    int* idx; float* wts;         // [T][top]
+};
+template <typename AT> __global__ void __launch_bounds__(256) moe_router_kernel(const MoeRouterParams<AT> p) {
+    extern __shared__ __align__(16) float mr_sm[];
+    float* hs = mr_sm;                       // [width]
+    float* score = hs + ((p.width + 3) & ~3);   // [E] sigmoid(logit)
+    float* choice = score + p.E;             // [E] score + correction; -inf once chosen
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const AT* h = p.h + (size_t)t * p.ld;
+    for (int c = threadIdx.x; c < p.width; c += blockDim.x) hs[c] = to_f(h[c]);
+    __syncthreads();
+    for (int e = warp; e < p.E; e += nw) {
+        const float* w = p.router + (size_t)e * p.width;
+        float a = 0.0f;
+        for (int c = lane; c < p.width; c += 32) a = fmaf(w[c], hs[c], a);
+        a = warp_sum(a);
+        if (lane == 0) { const float s = 1.0f / (1.0f + expf(-a)); score[e] = s; choice[e] = s + p.correction[e]; }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    float sum = 0.0f;
+    for (int k = 0; k < p.top; k++) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < p.E; e += 32)
+            if (choice[e] > best) { best = choice[e]; bi = e; }   // ascending e: the lowest index wins a tie inside a lane
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        const float s = score[bi];
+        sum += s;
+        if (lane == 0) { p.idx[(size_t)t * p.top + k] = bi; p.wts[(size_t)t * p.top + k] = s; choice[bi] = -INFINITY; }
+        __syncwarp();
+    }
+    const float f = p.scale / (sum + 1e-20f);
+    for (int k = lane; k < p.top; k += 32) p.wts[(size_t)t * p.top + k] *= f;
+}
+
+// n = T * top pairs.  One CTA: histogram, exclusive scan, placement.  Which pair of an expert gets which of the expert's
+// slots depends on the order the atomics land in; every row is computed on its own, so the results do not.
+struct MoeSortParams {
+    const int* idx; int n, E, top;
+    int* grp;       // [E + 1]
+    int* slot;      // [n]: slot of pair (t, k)
+    int* row_of;    // [n]: token of a slot
+};
+static __global__ void __launch_bounds__(1024) moe_sort_kernel(const MoeSortParams p) {
+    extern __shared__ int ms_sm[];   // [E] counts, then [E] cursors
+    int* cnt = ms_sm;
+    int* cur = cnt + p.E;
+    pdl_launch();
+    pdl_wait();
+    for (int e = threadIdx.x; e < p.E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < p.n; i += blockDim.x) atomicAdd(&cnt[p.idx[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int a = 0;
+        for (int e = 0; e < p.E; e++) { p.grp[e] = a; cur[e] = a; a += cnt[e]; }
+        p.grp[p.E] = a;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < p.n; i += blockDim.x) {
+        const int s = atomicAdd(&cur[p.idx[i]], 1);
+        p.slot[i] = s;
+        p.row_of[s] = i / p.top;
+    }
+}
+
+template <typename AT> struct MoeGatherParams {
+    const AT* h; int ld; const int* row_of; AT* out; int width;
+};
+template <typename AT> __global__ void __launch_bounds__(128) moe_gather_kernel(const MoeGatherParams<AT> p) {
+    pdl_launch();
+    pdl_wait();
+    const AT* src = p.h + (size_t)p.row_of[blockIdx.x] * p.ld;
+    AT* dst = p.out + (size_t)blockIdx.x * p.width;
+    for (int c = threadIdx.x; c < p.width; c += blockDim.x) dst[c] = src[c];
+}
+
+struct MoeCombineParams {
+    const float* y;           // [slots][width] expert outputs
+    const int* slot;          // [T][top] slot of every pair, or null: pair (t, k) sits in slot t*top + k
+    const float* wts;         // [T][top]
+    float* x; int ldx;        // residual stream
+    TanhNorm n;               // n.alpha null: x += sum;  else x += tanh(alpha * sum) * w + b
+    int top, width;
+};
+static __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombineParams p) {
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const float alpha = p.n.alpha ? *p.n.alpha : 0.0f;
+    for (int c = threadIdx.x; c < p.width; c += blockDim.x) {
+        float a = 0.0f;
+        for (int k = 0; k < p.top; k++) {
+            const int s = p.slot ? p.slot[(size_t)t * p.top + k] : t * p.top + k;
+            a = fmaf(p.wts[(size_t)t * p.top + k], p.y[(size_t)s * p.width + c], a);
+        }
+        p.x[(size_t)t * p.ldx + c] += p.n.alpha ? tanhnorm_apply(p.n, alpha, c, a) : a;
+    }
+}
+
+}  // namespace dense
+}  // namespace lmrs

@@ -21,6 +21,7 @@ class ModelType(IntEnum):  # src/transformer.rs:50-55
     LLAMA = 1
     PHI = 2
     GENETAR = 3   # a folder model (config.json + model.safetensors), not an LMRS file
+    TUDATAR = 4   # a folder model: delta-rule / latent-attention / windowed-attention layers with routed experts
 
 
 class QuantType(IntEnum):  # src/quantization.rs:1-6
