@@ -170,9 +170,10 @@ class Transformer:
         check(lib().lmrs_b200_last_prefill_device_ms(self._h, C.byref(ms)))
         return ms.value
 
-    def read_kv(self, layer: int, pos0: int, n: int):
+    def read_kv(self, layer: int, pos0: int, n: int, k_cols: int = 0, v_cols: int = 0):
+        """cached rows of a layer; folder models whose layers differ in size name the row widths of the layer they ask for"""
         kvd = self.args.head_size * self.args.n_kv_heads // self._world   # a sharded handle holds its own KV heads only
-        k, v = np.zeros((n, kvd), np.float32), np.zeros((n, kvd), np.float32)
+        k, v = np.zeros((n, k_cols or kvd), np.float32), np.zeros((n, v_cols or kvd), np.float32)
         check(lib().lmrs_b200_read_kv(self._h, layer, pos0, n, _vp(k), _vp(v)))
         return k, v
 

@@ -205,11 +205,18 @@ def window_mixer(h, W, p, m, eps, state, pos0):
 
 
 # ---- feed-forward: routed experts -----------------------------------------------------------------------------------------------------
+CHOICE_GAPS = []   # per route() call: the smallest distance between the last chosen and the first rejected expert
+
+
 def route(h, W, p, r):
     """(chosen experts [T, top], their weights [T, top])"""
     s = sigmoid(h @ W[p + "router"].T)
     choice = s + W[p + "correction"]
-    idx = np.argsort(-choice, axis=-1, kind="stable")[:, :r["top"]]
+    order = np.argsort(-choice, axis=-1, kind="stable")
+    idx = order[:, :r["top"]]
+    if r["top"] < choice.shape[-1]:
+        ranked = np.take_along_axis(choice, order, -1)
+        CHOICE_GAPS.append(float((ranked[:, r["top"] - 1] - ranked[:, r["top"]]).min()))
     w = np.take_along_axis(s, idx, -1)
     return idx, w / (w.sum(-1, keepdims=True) + 1e-20) * r["scale"]
 
@@ -263,6 +270,13 @@ class StepOracle:
 
 def forward(cfg, W, tokens):
     return StepOracle(cfg, W).step(tokens)
+
+
+def clear_choices(cfg, W, tokens, gap):
+    """True when no routing decision of this run is closer than `gap` (a test in reduced precision must not rest on one)"""
+    del CHOICE_GAPS[:]
+    forward(cfg, W, tokens)
+    return all(g > gap for g in CHOICE_GAPS)
 
 
 def rel_rms(got, want):
