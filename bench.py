@@ -140,6 +140,8 @@ def load_gemv_traffic(model, quant):
 
 def bench_arch(args):
     """--arch genetar: the folder-model architecture and the closest LMRS model (Llama, Q8_0) at the same layer shape, one GPU.
+    --arch tudatar: that architecture (delta-rule / windowed / latent attention layers, routed experts whose chosen experts
+    together are as wide as the dense feed-forward) and Genetar, the closest folder model, at the same layer shape.
     Prefill: device time (CUDA events on the handle's stream) of one pass over T prompt tokens.  Decode: device time of K
     HBM-resident steps at positions P.. after a P-token prompt, and the same loop end to end through forward_argmax.  Every
     step streams the whole weight set (larger than L2), so no flush is needed between steps."""
@@ -161,7 +163,7 @@ def bench_arch(args):
     except Exception:
         peak_tf, tf_src = 1590.0, "fallback 1.59 PFLOP/s"
     P, K, Wm = args.pos, args.steps, args.warmup
-    cap = max(lens + [P]) + K + Wm + 8
+    cap = max(lens + [P]) + 2 * (K + Wm) + 8
     stream = torch.cuda.Stream()
     sampler = ClockSampler(0); sampler.start()
 
@@ -177,56 +179,98 @@ def bench_arch(args):
 
     def decode_legs(m, vocab):
         toks = np.random.default_rng(2).integers(0, vocab, Wm + K)
+        # positions only ever advance: a model with recurrent layers cannot step back
         for i in range(Wm):
-            m.forward_device(int(toks[i]), P + (i % K))
+            m.forward_device(int(toks[i]), P + i)
         torch.cuda.synchronize()
         l0 = m.kernel_launches()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for i in range(K):
-            m.forward_device(int(toks[Wm + i]), P + i)
+            m.forward_device(int(toks[Wm + i]), P + Wm + i)
         e1.record(stream)
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / K
         launches = (m.kernel_launches() - l0) // K
         tok = 1
         for i in range(Wm):
-            tok = m.forward_argmax(tok, P + i)
+            tok = m.forward_argmax(tok, P + Wm + K + i)
         t0 = time.perf_counter()
         for i in range(K):
-            tok = m.forward_argmax(tok, P + i)
+            tok = m.forward_argmax(tok, P + 2 * Wm + K + i)
         e2e_ms = (time.perf_counter() - t0) / K * 1e3
         return ms, e2e_ms, launches
 
     out = {}
-    # ---- the folder model ---------------------------------------------------------------------------------------------
-    cfg = md.genetar_config(a.dim, a.hidden_dim, a.n_layers, a.n_heads, a.n_kv_heads, a.head_size, a.vocab_size)
-    tmp = tempfile.mkdtemp(prefix="genetar_bench_")
-    try:
-        md.write_random_genetar(tmp, cfg, seed=0)
-        m = lmrs_b200.Transformer.open(tmp, dtype="bfloat16", max_tokens=cap)
-    finally:
-        shutil.rmtree(tmp, ignore_errors=True)
-    m.set_stream(stream.cuda_stream)
     prompt = np.random.default_rng(1).integers(0, a.vocab_size, max(lens + [P]) + 1).astype(np.uint32)
-    flops_tok = md.genetar_matmul_flops_per_token(cfg) - 2 * a.vocab_size * a.dim   # the head runs on wanted rows only
-    pre = {}
-    for T in lens:
-        m.forward_tokens(prompt[:T], 0, [T - 1])
-        ms = timed(lambda: m.forward_tokens(prompt[:T], 0, [T - 1]), 3)
-        att = 4.0 * a.n_heads * a.head_size * T * (T + 1) / 2 * a.n_layers
-        fl = flops_tok * T + att
-        pre[str(T)] = {"ms": ms, "tok_s": T / ms * 1e3, "tflops": fl / ms / 1e9, "frac_of_bf16_peak": fl / ms / 1e9 / peak_tf,
-                       "matmul_flops": flops_tok * T, "attention_flops_f32": att}
-    m.forward_tokens(prompt[:P], 0, [])
-    ms, e2e_ms, launches = decode_legs(m, a.vocab_size)
-    kv = sum(2 * (P + K // 2) * L["mixer"]["kv_heads"] * L["mixer"]["dim"] * 4 for L in cfg["layers"])
-    by = md.genetar_param_bytes(cfg) + kv
-    out["genetar"] = {"dtype": "bf16 weights and operands, f32 accumulation, f32 KV cache", "weight_bytes": md.genetar_param_bytes(cfg),
-                      "prefill": pre, "decode": {"ms_per_step": ms, "tok_s": 1e3 / ms, "e2e_tok_s": 1e3 / e2e_ms, "launches_per_step": launches,
-                                                 "algorithmic_bytes_per_step": by, "gb_s": by / ms / 1e6, "frac_of_hbm_peak": by / ms / 1e6 / peak_hbm}}
-    gl = m.kernel_launches()
-    m.close()
+    launches_total = [0]
+
+    def folder_model(key, cfg, writer, flops_tok, core_flops, weight_bytes, cache_bytes, dtype_note):
+        tmp = tempfile.mkdtemp(prefix=key + "_bench_")
+        try:
+            writer(tmp, cfg, seed=0)
+            m = lmrs_b200.Transformer.open(tmp, dtype="bfloat16", max_tokens=cap)
+        finally:
+            shutil.rmtree(tmp, ignore_errors=True)
+        m.set_stream(stream.cuda_stream)
+        pre = {}
+        for T in lens:
+            m.forward_tokens(prompt[:T], 0, [T - 1])
+            ms = timed(lambda: m.forward_tokens(prompt[:T], 0, [T - 1]), 3)
+            fl = flops_tok * T + core_flops(T)
+            pre[str(T)] = {"ms": ms, "tok_s": T / ms * 1e3, "tflops": fl / ms / 1e9, "frac_of_bf16_peak": fl / ms / 1e9 / peak_tf,
+                           "matmul_flops": flops_tok * T, "mixer_core_flops_f32": core_flops(T)}
+        m.forward_tokens(prompt[:P], 0, [])
+        ms, e2e_ms, launches = decode_legs(m, a.vocab_size)
+        by = weight_bytes + cache_bytes
+        out[key] = {"dtype": dtype_note, "weight_bytes": weight_bytes,
+                    "prefill": pre, "decode": {"ms_per_step": ms, "tok_s": 1e3 / ms, "e2e_tok_s": 1e3 / e2e_ms, "launches_per_step": launches,
+                                               "algorithmic_bytes_per_step": by, "gb_s": by / ms / 1e6, "frac_of_hbm_peak": by / ms / 1e6 / peak_hbm}}
+        launches_total[0] += m.kernel_launches()
+        m.set_stream(0)
+        m.close()
+
+    gcfg = md.genetar_config(a.dim, a.hidden_dim, a.n_layers, a.n_heads, a.n_kv_heads, a.head_size, a.vocab_size)
+    head_flops = 2 * a.vocab_size * a.dim   # the head runs on wanted rows only
+    if args.arch == "tudatar":
+        top = 4
+        tcfg = md.tudatar_config(a.dim, a.n_layers, a.vocab_size, heads=a.n_heads, kv_heads=a.n_kv_heads, head_dim=a.head_size,
+                                 delta_heads=max(1, a.dim // 128), delta_dim=128, experts=args.arch_experts, top=top,
+                                 expert_ff=a.hidden_dim // top, window=1024, kv_rank=256, q_rank=768, rot_dim=64)
+        kvb = 0
+        for L in tcfg["layers"]:
+            mx = L["mixer"]
+            if L["type"] == "channel_delta":
+                kvb += 2 * mx["heads"] * mx["dim"] * mx["vdim"] * 4   # the state is read and written
+            elif L["type"] == "latent_attention":
+                kvb += (P + K // 2) * (mx["kv_rank"] + mx["rot_dim"]) * 4
+            else:
+                kvb += 2 * min(P + K // 2, mx["mask"]["size"]) * mx["kv_heads"] * mx["dim"] * 4
+        folder_model("tudatar", tcfg, md.write_random_tudatar, md.tudatar_matmul_flops_per_token(tcfg) - head_flops,
+                     lambda T: md.tudatar_mixer_flops(tcfg, T), md.tudatar_param_bytes(tcfg), kvb,
+                     "bf16 weights and operands, f32 accumulation; f32 caches, recurrent state, norms, router")
+    kv = sum(2 * (P + K // 2) * L["mixer"]["kv_heads"] * L["mixer"]["dim"] * 4 for L in gcfg["layers"])
+    folder_model("genetar", gcfg, md.write_random_genetar, md.genetar_matmul_flops_per_token(gcfg) - head_flops,
+                 lambda T: int(4.0 * a.n_heads * a.head_size * T * (T + 1) / 2 * a.n_layers), md.genetar_param_bytes(gcfg), kv,
+                 "bf16 weights and operands, f32 accumulation, f32 KV cache")
+    gl = launches_total[0]
+    if args.arch == "tudatar":
+        clocks = sampler.stop()
+        g = out["tudatar"]["decode"]
+        lt = [L["type"] for L in tcfg["layers"][:4]]
+        print(json.dumps({
+            "metric": f"decode tok/s Tudatar bf16 at the layer shape of {args.model} (prefill and Genetar of the same shape in 'arch')",
+            "value": g["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": Wm, "ms_per_step": g["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"model": f"Tudatar {a.n_layers} layers ({', '.join(lt)}, ...), width {a.dim}, {args.arch_experts} experts of ff {a.hidden_dim // 4}, 4 chosen, "
+                                f"{a.n_heads}/{a.n_kv_heads} heads of {a.head_size}, window 1024, latent 256+64, vocab {a.vocab_size}",
+                       "first_pos": P, "batch": 1, "prefill_lengths": lens,
+                       "l2": "inputs larger than L2 (the active weight set is streamed every step); no flush needed"},
+            "e2e": {"value": g["e2e_tok_s"], "unit": "tok/s", "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 4,
+                    "api": "forward_argmax(token, pos) -> next token"},
+            "gpu_launches": gl, "clocks": clocks, "peaks": {"hbm_gb_s": peak_hbm, "hbm_source": peak_src, "bf16_tflops": peak_tf, "bf16_source": tf_src},
+            "arch": out}))
+        return
     # ---- the closest LMRS model: Llama, Q8_0, same shape ----------------------------------------------------------------------
     buf = lf.write_synthetic(a, seed=0, mode="fast")
     m, _ = lmrs_b200.Transformer.new(buf, 0)
@@ -278,7 +322,8 @@ def main():
     ap.add_argument("--pos", type=int, default=512, help="prompt length / first decode position")
     ap.add_argument("--cpu-steps", type=int, default=16, help="decode steps of the bounded cpu_baseline sample")
     ap.add_argument("--parity-steps", type=int, default=4, help="greedy decode steps replayed on the CPU oracle (0: skip the parity block)")
-    ap.add_argument("--arch", default="", choices=["", "genetar"],
+    ap.add_argument("--arch-experts", type=int, default=16, help="--arch tudatar: experts per layer (4 are chosen)")
+    ap.add_argument("--arch", default="", choices=["", "genetar", "tudatar"],
                     help="instead of the default workload: prefill and decode throughput of this folder-model architecture (random "
                          "bf16 weights at the layer shape of --model) beside the LMRS Q8_0 Llama of the same shape")
     ap.add_argument("--arch-layers", type=int, default=0, help="--arch: number of layers (0: as many as --model has)")

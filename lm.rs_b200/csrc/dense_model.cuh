@@ -298,14 +298,17 @@ template <typename AT, typename WT> class DenseModel : public ArchModel {
         const int kv_mul = p.H / p.G, T = p.T;
         p.part = part;
         p.HC = std::min(kv_mul, 16);
+        int tiles = (int)((pos_hint + 1 + ATT_KT - 1) / ATT_KT);
+        if (p.window > 0) tiles = std::min(tiles, (p.window + ATT_KT - 2) / ATT_KT + 1);   // tiles a window can touch
+        tiles = std::min(tiles, MAX_SPLIT);
+        // a one-row step over few KV heads: fewer query heads per CTA, so that more SMs share the keys
+        while (T == 1 && p.HC > 4 && p.G * ((kv_mul + p.HC - 1) / p.HC) * tiles < sms) p.HC /= 2;
         const int chunks = (kv_mul + p.HC - 1) / p.HC;
         int rw = 4;
         if (T == 1) rw = p.HC <= 4 ? 1 : (p.HC <= 8 ? 2 : 4);
         p.TQ = std::max(1, rw * ATT_WARPS / p.HC);
         p.nsplit = 1;
         if (T == 1) {   // decode: split the keys so that the GPU has enough CTAs
-            int tiles = (int)((pos_hint + 1 + ATT_KT - 1) / ATT_KT);
-            if (p.window > 0) tiles = std::min(tiles, (p.window + ATT_KT - 2) / ATT_KT + 1);   // tiles a window can touch
             p.nsplit = std::max(1, std::min({tiles, MAX_SPLIT, (2 * sms) / std::max(1, p.G * chunks)}));
         }
         const int gx = (T + p.TQ - 1) / p.TQ, gy = p.G * chunks;

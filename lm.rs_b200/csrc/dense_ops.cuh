@@ -754,15 +754,21 @@ template <typename AT> __global__ void __launch_bounds__(128) attn_combine_kerne
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (r >= p.rows) return;
     const float* src = p.part + (size_t)r * p.nsplit * (p.dv + 2);
-    float mx = -1e30f;
-    for (int s = 0; s < p.nsplit; s++) mx = fmaxf(mx, src[(size_t)s * (p.dv + 2)]);
-    float l = 0.0f;
-    for (int s = 0; s < p.nsplit; s++) l += src[(size_t)s * (p.dv + 2) + 1] * expf(src[(size_t)s * (p.dv + 2)] - mx);
+    // lane s holds split s (nsplit <= 32): its weight exp(m_s - max) is computed once and handed round by shuffles
+    const float ms = lane < p.nsplit ? src[(size_t)lane * (p.dv + 2)] : -1e30f;
+    const float mx = warp_max(ms);
+    const float ws = lane < p.nsplit ? expf(ms - mx) : 0.0f;
+    const float l = warp_sum(lane < p.nsplit ? src[(size_t)lane * (p.dv + 2) + 1] * ws : 0.0f);
     const float gt = p.gate ? p.gate[r] : 1.0f;
-    for (int c = lane; c < p.dv; c += 32) {
+    const float inv = gt / l;
+    for (int c0 = 0; c0 < p.dv; c0 += 32) {
+        const int c = c0 + lane;
         float a = 0.0f;
-        for (int s = 0; s < p.nsplit; s++) a += src[(size_t)s * (p.dv + 2) + 2 + c] * expf(src[(size_t)s * (p.dv + 2)] - mx);
-        from_f(p.out[(size_t)r * p.dv + c], a * (gt / l));
+        for (int s = 0; s < p.nsplit; s++) {
+            const float w = __shfl_sync(0xffffffffu, ws, s);
+            if (c < p.dv) a = fmaf(src[(size_t)s * (p.dv + 2) + 2 + c], w, a);
+        }
+        if (c < p.dv) from_f(p.out[(size_t)r * p.dv + c], a * inv);
     }
 }
 

@@ -204,17 +204,34 @@ static __global__ void __launch_bounds__(256) conv_tail_update_kernel(const Conv
         if (r < p.taps - 1) p.tail[(size_t)r * p.C + c] = nv[r];
 }
 
+// decay per (token, head, key channel) from the projected logits, in place: g = exp(-exp(a_log[head]) * softplus(logit))
+struct DeltaDecayParams {
+    float* a;              // [T][H*dk] logits in, decays out
+    const float* a_log;    // [H]
+    int n, H, dk;          // n = T * H * dk
+};
+static __global__ void __launch_bounds__(256) delta_decay_kernel(const DeltaDecayParams p) {
+    pdl_launch();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= p.n) return;
+    const float a = p.a[i];
+    const float sp = a > 20.0f ? a : log1pf(expf(a));
+    p.a[i] = expf(-expf(p.a_log[(i / p.dk) % p.H]) * sp);
+}
+
 // The scan.  CTA = (block of state columns, head); a column j of the head's state S [dk][dv] belongs to `lpc` adjacent lanes,
-// lane s of them holding rows s, s + lpc, ... (at most DELTA_NR each) in registers.  Columns never interact: S^T k and S^T q
-// are sums down a column, the rank-one update adds k_i u_j.  Tokens are staged DELTA_TB at a time in shared memory (q, k, the
-// decays computed from the projected logits, v, beta); then every token costs two passes over the registers and two
+// lane s of them holding DELTA_NR rows in registers: groups of four consecutive rows, group r4 at rows (r4*lpc + s)*4 .., so a
+// lane reads its q, k and decay entries of a token with 16-byte shared-memory loads that do not collide with its neighbours'.
+// Columns never interact: S^T k and S^T q are sums down a column, the rank-one update adds k_i u_j.  Tokens are staged
+// DELTA_TB at a time in shared memory by cp.async (q, k, decays, v, beta), the next block in flight while this one is used;
+// rows beyond dk are zero-filled, so the arithmetic needs no bounds.  Every token costs two passes over the registers and two
 // reductions across the lpc lanes.  The order of every sum is fixed, so a token's result does not depend on the portion it
 // arrives in.  The state is read at the start (zeros when the step starts at position 0) and written back at the end.
 constexpr int DELTA_NR = 16, DELTA_TB = 8, DELTA_THREADS = 128;
 struct DeltaScanParams {
     const float* qkv; int ld;   // [T][C]: q at 0, k at G*dk, v at 2*G*dk
-    const float* araw;          // [T][H*dk]: decay logits (second low-rank projection + bias)
-    const float* a_log;         // [H]
+    const float* decay;         // [T][H*dk]
     const float* beta;          // [T][H]
     float* state;               // [H][dk][dv]
     float* out;                 // [T][H*dv]
@@ -222,70 +239,105 @@ struct DeltaScanParams {
     PosSrc ps;
 };
 inline int delta_lanes_per_column(int dk) { int l = 1; while (l * DELTA_NR < dk) l *= 2; return l; }   // dk <= 32 * DELTA_NR
-inline size_t delta_scan_smem(int dk, int lpc) { return (size_t)DELTA_TB * (3 * dk + DELTA_THREADS / lpc + 1) * 4; }
+inline size_t delta_scan_smem(int lpc) { return (size_t)2 * DELTA_TB * (3 * DELTA_NR * lpc + DELTA_THREADS / lpc + 4) * 4; }
+DN_DEVINL void cp_async4_zfill(void* smem_dst, const void* gsrc, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const int n = valid ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
+}
 static __global__ void __launch_bounds__(DELTA_THREADS) delta_scan_kernel(const DeltaScanParams p) {
-    extern __shared__ float ds_sm[];
+    extern __shared__ __align__(16) float ds_sm[];
     pdl_launch();
     pdl_wait();
-    const int cols = DELTA_THREADS / p.lpc;
-    float* qs = ds_sm;                          // [TB][dk]
-    float* ks = qs + DELTA_TB * p.dk;
-    float* gs = ks + DELTA_TB * p.dk;
-    float* vs = gs + DELTA_TB * p.dk;           // [TB][cols]
-    float* bs = vs + DELTA_TB * cols;           // [TB]
+    const int cols = DELTA_THREADS / p.lpc, dkp = DELTA_NR * p.lpc;   // dkp: rows the lanes cover (>= dk, a multiple of 4)
+    const int blk = DELTA_TB * (3 * dkp + cols + 4);                   // floats per staging buffer
     const int h = blockIdx.y, g = h / (p.H / p.G);
     const int s = threadIdx.x % p.lpc, jl = threadIdx.x / p.lpc, j = blockIdx.x * cols + jl;
     const bool col_ok = j < p.dv;
     const uint32_t pos0 = pos_of(p.ps);
+    const int vq = 2 * p.G * p.dk;
+    // 16-byte copies when every row piece starts on a 16-byte boundary
+    const bool vec = (p.dk & 3) == 0 && (p.ld & 3) == 0 && ((p.H * p.dk) & 3) == 0;
+    auto stage = [&](int t0, int buf) {
+        float* qs = ds_sm + (size_t)buf * blk;     // [TB][dkp]
+        float* ks = qs + DELTA_TB * dkp;
+        float* gs = ks + DELTA_TB * dkp;
+        float* vs = gs + DELTA_TB * dkp;           // [TB][cols]
+        float* bs = vs + DELTA_TB * cols;          // [TB]
+        const int nt = min(DELTA_TB, p.T - t0);
+        if (vec) {
+            const int q4 = dkp >> 2;
+            for (int e = threadIdx.x; e < nt * q4; e += blockDim.x) {
+                const int tt = e / q4, i = (e - tt * q4) << 2;
+                const bool ok = i < p.dk;
+                const float* row = p.qkv + (size_t)(t0 + tt) * p.ld;
+                cp_async16_zfill(qs + tt * dkp + i, ok ? row + g * p.dk + i : p.qkv, ok);
+                cp_async16_zfill(ks + tt * dkp + i, ok ? row + (p.G + g) * p.dk + i : p.qkv, ok);
+                cp_async16_zfill(gs + tt * dkp + i, ok ? p.decay + ((size_t)(t0 + tt) * p.H + h) * p.dk + i : p.qkv, ok);
+            }
+        } else {
+            for (int e = threadIdx.x; e < nt * dkp; e += blockDim.x) {
+                const int tt = e / dkp, i = e - tt * dkp;
+                const bool ok = i < p.dk;
+                const float* row = p.qkv + (size_t)(t0 + tt) * p.ld;
+                cp_async4_zfill(qs + tt * dkp + i, ok ? row + g * p.dk + i : p.qkv, ok);
+                cp_async4_zfill(ks + tt * dkp + i, ok ? row + (p.G + g) * p.dk + i : p.qkv, ok);
+                cp_async4_zfill(gs + tt * dkp + i, ok ? p.decay + ((size_t)(t0 + tt) * p.H + h) * p.dk + i : p.qkv, ok);
+            }
+        }
+        for (int e = threadIdx.x; e < nt * cols; e += blockDim.x) {
+            const int tt = e / cols, c = e - tt * cols, jj = blockIdx.x * cols + c;
+            cp_async4_zfill(vs + e, jj < p.dv ? p.qkv + (size_t)(t0 + tt) * p.ld + vq + h * p.dv + jj : p.qkv, jj < p.dv);
+        }
+        if (threadIdx.x < nt) cp_async4_zfill(bs + threadIdx.x, p.beta + (size_t)(t0 + threadIdx.x) * p.H + h, true);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    stage(0, 0);
     float S[DELTA_NR];
     float* sp = p.state + ((size_t)h * p.dk) * p.dv + j;
 #pragma unroll
     for (int r = 0; r < DELTA_NR; r++) {
-        const int i = s + r * p.lpc;
+        const int i = ((r >> 2) * p.lpc + s) * 4 + (r & 3);
         S[r] = (pos0 > 0 && col_ok && i < p.dk) ? sp[(size_t)i * p.dv] : 0.0f;
     }
-    const float rate = expf(p.a_log[h]);
-    const int vq = 2 * p.G * p.dk;
-    for (int t0 = 0; t0 < p.T; t0 += DELTA_TB) {
+    int buf = 0;
+    for (int t0 = 0; t0 < p.T; t0 += DELTA_TB, buf ^= 1) {
         const int nt = min(DELTA_TB, p.T - t0);
-        __syncthreads();   // the previous block of tokens is consumed
-        for (int e = threadIdx.x; e < nt * p.dk; e += blockDim.x) {
-            const int tt = e / p.dk, i = e - tt * p.dk;
-            const float* row = p.qkv + (size_t)(t0 + tt) * p.ld;
-            qs[tt * p.dk + i] = row[g * p.dk + i];
-            ks[tt * p.dk + i] = row[(p.G + g) * p.dk + i];
-            const float a = p.araw[((size_t)(t0 + tt) * p.H + h) * p.dk + i];
-            const float sp_a = a > 20.0f ? a : log1pf(expf(a));
-            gs[tt * p.dk + i] = expf(-rate * sp_a);
-        }
-        for (int e = threadIdx.x; e < nt * cols; e += blockDim.x) {
-            const int tt = e / cols, c = e - tt * cols, jj = blockIdx.x * cols + c;
-            vs[e] = jj < p.dv ? p.qkv[(size_t)(t0 + tt) * p.ld + vq + h * p.dv + jj] : 0.0f;
-        }
-        if (threadIdx.x < nt) bs[threadIdx.x] = p.beta[(size_t)(t0 + threadIdx.x) * p.H + h];
-        __syncthreads();
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();   // this block has landed for everyone, and everyone is done with the other buffer
+        if (t0 + DELTA_TB < p.T) stage(t0 + DELTA_TB, buf ^ 1);
+        const float* qs = ds_sm + (size_t)buf * blk;
+        const float* ks = qs + DELTA_TB * dkp;
+        const float* gs = ks + DELTA_TB * dkp;
+        const float* vs = gs + DELTA_TB * dkp;
+        const float* bs = vs + DELTA_TB * cols;
         for (int tt = 0; tt < nt; tt++) {
-            const float* kq = ks + tt * p.dk;
-            const float* qq = qs + tt * p.dk;
-            const float* gq = gs + tt * p.dk;
-            float r0 = 0.0f, r1 = 0.0f;
+            float kk[DELTA_NR];
+            float r0 = 0.0f, r1 = 0.0f, r2 = 0.0f, r3 = 0.0f;
 #pragma unroll
-            for (int r = 0; r < DELTA_NR; r += 2) {
-                const int i0 = s + r * p.lpc, i1 = i0 + p.lpc;
-                if (i0 < p.dk) { S[r] *= gq[i0]; r0 = fmaf(S[r], kq[i0], r0); }
-                if (i1 < p.dk) { S[r + 1] *= gq[i1]; r1 = fmaf(S[r + 1], kq[i1], r1); }
+            for (int r4 = 0; r4 < DELTA_NR / 4; r4++) {
+                const int i = (r4 * p.lpc + s) * 4;
+                const float4 g4 = *reinterpret_cast<const float4*>(gs + tt * dkp + i);
+                const float4 k4 = *reinterpret_cast<const float4*>(ks + tt * dkp + i);
+                kk[4 * r4] = k4.x; kk[4 * r4 + 1] = k4.y; kk[4 * r4 + 2] = k4.z; kk[4 * r4 + 3] = k4.w;
+                S[4 * r4] *= g4.x; S[4 * r4 + 1] *= g4.y; S[4 * r4 + 2] *= g4.z; S[4 * r4 + 3] *= g4.w;
+                r0 = fmaf(S[4 * r4], k4.x, r0); r1 = fmaf(S[4 * r4 + 1], k4.y, r1);
+                r2 = fmaf(S[4 * r4 + 2], k4.z, r2); r3 = fmaf(S[4 * r4 + 3], k4.w, r3);
             }
-            float rsum = r0 + r1;
+            float rsum = (r0 + r1) + (r2 + r3);
             for (int o = p.lpc >> 1; o > 0; o >>= 1) rsum += __shfl_xor_sync(0xffffffffu, rsum, o);
             const float u = bs[tt] * (vs[tt * cols + jl] - rsum);
-            float o0 = 0.0f, o1 = 0.0f;
+            float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
 #pragma unroll
-            for (int r = 0; r < DELTA_NR; r += 2) {
-                const int i0 = s + r * p.lpc, i1 = i0 + p.lpc;
-                if (i0 < p.dk) { S[r] = fmaf(kq[i0], u, S[r]); o0 = fmaf(S[r], qq[i0], o0); }
-                if (i1 < p.dk) { S[r + 1] = fmaf(kq[i1], u, S[r + 1]); o1 = fmaf(S[r + 1], qq[i1], o1); }
+            for (int r4 = 0; r4 < DELTA_NR / 4; r4++) {
+                const int i = (r4 * p.lpc + s) * 4;
+                const float4 q4 = *reinterpret_cast<const float4*>(qs + tt * dkp + i);
+                S[4 * r4] = fmaf(kk[4 * r4], u, S[4 * r4]); S[4 * r4 + 1] = fmaf(kk[4 * r4 + 1], u, S[4 * r4 + 1]);
+                S[4 * r4 + 2] = fmaf(kk[4 * r4 + 2], u, S[4 * r4 + 2]); S[4 * r4 + 3] = fmaf(kk[4 * r4 + 3], u, S[4 * r4 + 3]);
+                o0 = fmaf(S[4 * r4], q4.x, o0); o1 = fmaf(S[4 * r4 + 1], q4.y, o1);
+                o2 = fmaf(S[4 * r4 + 2], q4.z, o2); o3 = fmaf(S[4 * r4 + 3], q4.w, o3);
             }
-            float osum = o0 + o1;
+            float osum = (o0 + o1) + (o2 + o3);
             for (int o = p.lpc >> 1; o > 0; o >>= 1) osum += __shfl_xor_sync(0xffffffffu, osum, o);
             if (s == 0 && col_ok) p.out[(size_t)(t0 + tt) * p.H * p.dv + (size_t)h * p.dv + j] = osum;
         }
@@ -293,7 +345,7 @@ static __global__ void __launch_bounds__(DELTA_THREADS) delta_scan_kernel(const 
     if (col_ok) {
 #pragma unroll
         for (int r = 0; r < DELTA_NR; r++) {
-            const int i = s + r * p.lpc;
+            const int i = ((r >> 2) * p.lpc + s) * 4 + (r & 3);
             if (i < p.dk) sp[(size_t)i * p.dv] = S[r];
         }
     }

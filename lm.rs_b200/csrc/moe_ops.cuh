@@ -1,6 +1,7 @@
 // moe_ops.cuh -- a feed-forward made of routed experts, around the matrix kernels of dense_ops.cuh / dense_gemm.cuh:
-//   moe_router_kernel    router logits in f32 (f32 router matrix), score = sigmoid(logit), the `top` experts with the largest
-//                        score + correction[e] are chosen, their weights are score / (sum of chosen scores + 1e-20) * scale
+//   moe_logits_kernel    router logits in f32 (f32 router matrix)
+//   moe_topk_kernel      score = sigmoid(logit), the `top` experts with the largest score + correction[e] are chosen, their
+//                        weights are score / (sum of chosen scores + 1e-20) * scale
 //   moe_sort_kernel      (token, choice) pairs counted and sorted by expert: row offsets per expert, the slot of every pair,
 //                        the token of every slot
 //   moe_gather_kernel    the normalised rows copied into expert order (the grouped matrix kernels then see one contiguous row
@@ -15,33 +16,49 @@ namespace lmrs {
 namespace dense {
 
 template <typename AT> struct MoeRouterParams {
-    const AT* h; int ld;          // [T][width] normalised input (operand type)
+    const AT* h; int ld;          // [T][width] normalised input (operand type), or null:
+    const float* x; TanhNorm tn;  // ... the residual row, normalised here (tanh norm) and rounded to the operand type
     const float* router;          // [E][width]
     const float* correction;      // [E], added for the choice only
     int E, top, width;
     float scale;
+    float* z;                     // [T][E] router logits (scratch between the two kernels)
     int* idx; float* wts;         // [T][top]
 };
-template <typename AT> __global__ void __launch_bounds__(256) moe_router_kernel(const MoeRouterParams<AT> p) {
-    extern __shared__ __align__(16) float mr_sm[];
-    float* hs = mr_sm;                       // [width]
-    float* score = hs + ((p.width + 3) & ~3);   // [E] sigmoid(logit)
-    float* choice = score + p.E;             // [E] score + correction; -inf once chosen
+// logits: one warp per (token, expert), so that a single token still spreads over E warps on many SMs
+template <typename AT> __global__ void __launch_bounds__(128) moe_logits_kernel(const MoeRouterParams<AT> p) {
     pdl_launch();
     pdl_wait();
-    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    const AT* h = p.h + (size_t)t * p.ld;
-    for (int c = threadIdx.x; c < p.width; c += blockDim.x) hs[c] = to_f(h[c]);
-    __syncthreads();
-    for (int e = warp; e < p.E; e += nw) {
-        const float* w = p.router + (size_t)e * p.width;
-        float a = 0.0f;
-        for (int c = lane; c < p.width; c += 32) a = fmaf(w[c], hs[c], a);
-        a = warp_sum(a);
-        if (lane == 0) { const float s = 1.0f / (1.0f + expf(-a)); score[e] = s; choice[e] = s + p.correction[e]; }
+    const int t = blockIdx.x, lane = threadIdx.x & 31;
+    const int e = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (e >= p.E) return;
+    const float* w = p.router + (size_t)e * p.width;
+    float a = 0.0f;
+    if (p.h) {
+        const AT* h = p.h + (size_t)t * p.ld;
+        for (int c = lane; c < p.width; c += 32) a = fmaf(w[c], to_f(h[c]), a);
+    } else {
+        const float* x = p.x + (size_t)t * p.ld;
+        const float alpha = *p.tn.alpha;
+        for (int c = lane; c < p.width; c += 32) { AT r; from_f(r, tanhnorm_apply(p.tn, alpha, c, x[c])); a = fmaf(w[c], to_f(r), a); }
     }
-    __syncthreads();
-    if (warp != 0) return;
+    a = warp_sum(a);
+    if (lane == 0) p.z[(size_t)t * p.E + e] = a;
+}
+// choice: one warp per token
+template <typename AT> __global__ void __launch_bounds__(32) moe_topk_kernel(const MoeRouterParams<AT> p) {
+    extern __shared__ __align__(16) float mr_sm[];
+    float* score = mr_sm;            // [E] sigmoid(logit)
+    float* choice = score + p.E;     // [E] score + correction; -inf once chosen
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x, lane = threadIdx.x;
+    for (int e = lane; e < p.E; e += 32) {
+        const float sg = 1.0f / (1.0f + expf(-p.z[(size_t)t * p.E + e]));
+        score[e] = sg;
+        choice[e] = sg + p.correction[e];
+    }
+    __syncwarp();
     float sum = 0.0f;
     for (int k = 0; k < p.top; k++) {
         float best = -INFINITY;
@@ -54,9 +71,9 @@ template <typename AT> __global__ void __launch_bounds__(256) moe_router_kernel(
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
         }
-        const float s = score[bi];
-        sum += s;
-        if (lane == 0) { p.idx[(size_t)t * p.top + k] = bi; p.wts[(size_t)t * p.top + k] = s; choice[bi] = -INFINITY; }
+        const float sg = score[bi];
+        sum += sg;
+        if (lane == 0) { p.idx[(size_t)t * p.top + k] = bi; p.wts[(size_t)t * p.top + k] = sg; choice[bi] = -INFINITY; }
         __syncwarp();
     }
     const float f = p.scale / (sum + 1e-20f);
@@ -118,7 +135,7 @@ static __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombin
     pdl_wait();
     const int t = blockIdx.x;
     const float alpha = p.n.alpha ? *p.n.alpha : 0.0f;
-    for (int c = threadIdx.x; c < p.width; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < p.width; c += gridDim.y * blockDim.x) {
         float a = 0.0f;
         for (int k = 0; k < p.top; k++) {
             const int s = p.slot ? p.slot[(size_t)t * p.top + k] : t * p.top + k;

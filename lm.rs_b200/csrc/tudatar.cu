@@ -104,7 +104,7 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
     uint32_t next_pos = 0;       // where that state stands
     // scratch for `cap` rows
     AT *h = nullptr, *lat = nullptr, *qn = nullptr, *att = nullptr, *att2 = nullptr, *xg = nullptr, *act = nullptr;
-    float *proj = nullptr, *qa = nullptr, *qb = nullptr, *fa = nullptr, *fb = nullptr, *beta = nullptr, *part = nullptr, *y = nullptr, *wts = nullptr;
+    float *rz = nullptr, *proj = nullptr, *qa = nullptr, *qb = nullptr, *fa = nullptr, *fb = nullptr, *beta = nullptr, *part = nullptr, *y = nullptr, *wts = nullptr;
     int *eidx = nullptr, *slot = nullptr, *row_of = nullptr, *grp = nullptr;
     int max_proj = 0, max_lat = 0, max_qn = 0, max_att = 0, max_att2 = 0, max_qa = 0, max_qb = 0, max_fa = 0, max_fb = 0, max_H = 0,
         max_dv = 0, max_top = 0, max_ff = 0, max_E = 0;
@@ -338,7 +338,7 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
         drop_graphs();   // captured launches point into the old scratch
         for (void* p : {(void*)x, (void*)hn, (void*)d_rows, (void*)h, (void*)lat, (void*)qn, (void*)att, (void*)att2, (void*)xg, (void*)act, (void*)proj,
                         (void*)qa, (void*)qb, (void*)fa, (void*)fb, (void*)beta, (void*)part, (void*)y, (void*)wts, (void*)eidx, (void*)slot, (void*)row_of,
-                        (void*)grp})
+                        (void*)grp, (void*)rz})
             dfree(p);
         cap = 0;
         const size_t pairs = rows * std::max(max_top, 1);
@@ -348,7 +348,7 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
             dalloc(&qb, rows * std::max(max_qb, 1)) || dalloc(&fa, rows * std::max(max_fa, 1)) || dalloc(&fb, rows * std::max(max_fb, 1)) ||
             dalloc(&beta, rows * max_H) || dalloc(&part, (size_t)max_H * MAX_SPLIT * (max_dv + 2)) || dalloc(&xg, pairs * width) ||
             dalloc(&act, pairs * std::max(max_ff, 1)) || dalloc(&y, pairs * width) || dalloc(&wts, pairs) || dalloc(&eidx, pairs) ||
-            dalloc(&slot, pairs) || dalloc(&row_of, pairs) || dalloc(&grp, (size_t)max_E + 1))
+            dalloc(&slot, pairs) || dalloc(&row_of, pairs) || dalloc(&grp, (size_t)max_E + 1) || dalloc(&rz, rows * std::max(max_E, 1)))
             return 1;
         cap = rows;
         return 0;
@@ -366,6 +366,18 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
     }
 
     // ---- the layers -----------------------------------------------------------------------------------------------------------
+    // the mixer's fused input projection of N1(x): proj = N1(x) . w_in^T (+ bias).  One row: the norm is the prologue of the
+    // streaming kernel; many rows: h <- N1(x) first
+    int in_proj(cudaStream_t st, const Layer& L, int T) {
+        EpiParams<AT> e{}; e.out = proj; e.ldo = L.in_rows; e.scale = 1.0f; e.bias = L.b_in;
+        if (T == 1) {
+            GemvRowsParams<AT, WT> p{};
+            p.x = x; p.tn = L.n1.view(); p.w = L.w_in; p.K = width; p.O = L.in_rows; p.e = e;
+            return this->template launch_gemv<EPI_STORE, NORM_TANH>(st, p);
+        }
+        if (norm_rows(st, T, L.n1)) return 1;
+        return this->template matmul<EPI_STORE>(st, T, h, width, L.w_in, nullptr, width, L.in_rows, e);
+    }
     // h <- N(x) in the operand type
     int norm_rows(cudaStream_t st, int T, const Norm& n) {
         TanhNormRowsParams<AT> p{};
@@ -381,8 +393,7 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
 
     int mixer_window(cudaStream_t st, const Layer& L, int T, const PosSrc& ps, uint32_t pos_hint) {
         const LayerCfg& c = L.c;
-        EpiParams<AT> e{}; e.out = proj; e.ldo = L.in_rows; e.scale = 1.0f; e.bias = L.b_in;
-        if (this->template matmul<EPI_STORE>(st, T, h, width, L.w_in, nullptr, width, L.in_rows, e)) return 1;
+        if (in_proj(st, L, T)) return 1;
         QkvJointNormParams np{};
         np.qkv = proj; np.ld = L.in_rows; np.H = c.H; np.G = c.G; np.dk = c.dk; np.dv = c.dv; np.wq = L.qnorm; np.wk = L.knorm; np.eps = info.eps;
         np.q_out = qa; np.kcache = L.kcache; np.vcache = L.vcache; np.ps = ps;
@@ -398,8 +409,7 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
     int mixer_latent(cudaStream_t st, const Layer& L, int T, const PosSrc& ps, uint32_t pos_hint) {
         const LayerCfg& c = L.c;
         const int dq = c.dk + c.dr, dl = c.rk + c.dr;
-        EpiParams<AT> e{}; e.out = proj; e.ldo = L.in_rows; e.scale = 1.0f;
-        if (this->template matmul<EPI_STORE>(st, T, h, width, L.w_in, nullptr, width, L.in_rows, e)) return 1;
+        if (in_proj(st, L, T)) return 1;
         LatentKvPostParams<AT> kp{};
         kp.in = proj; kp.ld = L.in_rows; kp.rq = c.rq; kp.rk = c.rk; kp.dr = c.dr; kp.wq = L.dq_norm; kp.wkv = L.dkv_norm; kp.eps = info.eps;
         kp.rot_dims = c.rot.dims; kp.rot_cos = L.rot_cos; kp.rot_sin = L.rot_sin; kp.cq_out = lat; kp.cache = L.lcache; kp.ps = ps;
@@ -426,8 +436,7 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
     int mixer_delta(cudaStream_t st, const Layer& L, int T, const PosSrc& ps) {
         const LayerCfg& c = L.c;
         const int nqk = c.G * c.dk, nv = c.H * c.dv, C = 2 * nqk + nv;
-        EpiParams<AT> e{}; e.out = proj; e.ldo = L.in_rows; e.scale = 1.0f;
-        if (this->template matmul<EPI_STORE>(st, T, h, width, L.w_in, nullptr, width, L.in_rows, e)) return 1;
+        if (in_proj(st, L, T)) return 1;
         AT* a_lat = lat;
         AT* g_lat = lat + (size_t)cap * c.ra;
         DeltaPreParams<AT> pp{};
@@ -448,11 +457,14 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
         if (this->template matmul<EPI_STORE>(st, T, a_lat, c.ra, L.wa2, nullptr, c.ra, c.H * c.dk, ea)) return 1;
         EpiParams<AT> eg{}; eg.out = graw; eg.ldo = nv; eg.scale = 1.0f;
         if (this->template matmul<EPI_STORE>(st, T, g_lat, c.rg, L.wg2, nullptr, c.rg, nv, eg)) return 1;
+        DeltaDecayParams dp{};
+        dp.a = araw; dp.a_log = L.a_log; dp.n = T * c.H * c.dk; dp.H = c.H; dp.dk = c.dk;
+        if (launch_k("delta_decay_kernel", st, pdl_now, delta_decay_kernel, dim3((dp.n + 255) / 256), dim3(256), 0, dp)) return 1;
         DeltaScanParams sp{};
-        sp.qkv = qa; sp.ld = C; sp.araw = araw; sp.a_log = L.a_log; sp.beta = beta; sp.state = L.state; sp.out = o;
+        sp.qkv = qa; sp.ld = C; sp.decay = araw; sp.beta = beta; sp.state = L.state; sp.out = o;
         sp.T = T; sp.H = c.H; sp.G = c.G; sp.dk = c.dk; sp.dv = c.dv; sp.lpc = delta_lanes_per_column(c.dk); sp.ps = ps;
         const int cols = DELTA_THREADS / sp.lpc;
-        const size_t smem = delta_scan_smem(c.dk, sp.lpc);
+        const size_t smem = delta_scan_smem(sp.lpc);
         if (optin(delta_scan_kernel, smem)) return 1;
         if (launch_k("delta_scan_kernel", st, pdl_now, delta_scan_kernel, dim3((c.dv + cols - 1) / cols, c.H), dim3(DELTA_THREADS), smem, sp)) return 1;
         GatedHeadNormParams<AT> gp{};
@@ -463,20 +475,22 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
 
     int experts(cudaStream_t st, const Layer& L, int T) {
         const MoeCfg& f = L.c.moe;
+        // one row: the norm N2 is applied inside the kernels that read x (router logits, gate/up products); many rows: h <- N2(x)
+        if (T > 1 && norm_rows(st, T, L.n2)) return 1;
         MoeRouterParams<AT> rp{};
-        rp.h = h; rp.ld = width; rp.router = L.router; rp.correction = L.correction; rp.E = f.E; rp.top = f.top; rp.width = width; rp.scale = f.scale;
-        rp.idx = eidx; rp.wts = wts;
-        const size_t rsm = ((size_t)((width + 3) & ~3) + 2 * (size_t)f.E) * 4;
-        if (optin(moe_router_kernel<AT>, rsm)) return 1;
-        if (launch_k("moe_router_kernel", st, pdl_now, moe_router_kernel<AT>, dim3(T), dim3(256), rsm, rp)) return 1;
+        rp.h = T > 1 ? h : nullptr; rp.x = x; rp.tn = L.n2.view(); rp.ld = width; rp.router = L.router; rp.correction = L.correction;
+        rp.E = f.E; rp.top = f.top; rp.width = width; rp.scale = f.scale; rp.z = rz; rp.idx = eidx; rp.wts = wts;
+        if (launch_k("moe_logits_kernel", st, pdl_now, moe_logits_kernel<AT>, dim3(T, (f.E + 3) / 4), dim3(128), 0, rp)) return 1;
+        if (launch_k("moe_topk_kernel", st, pdl_now, moe_topk_kernel<AT>, dim3(T), dim3(32), (size_t)2 * f.E * 4, rp)) return 1;
         MoeCombineParams cp{};
         cp.y = y; cp.wts = wts; cp.x = x; cp.ldx = width; cp.n = L.n2b.view(); cp.top = f.top; cp.width = width;
         EpiParams<AT> eg{}; eg.act = act; eg.lda = f.ff;
         EpiParams<AT> ed{}; ed.out = y; ed.ldo = width; ed.scale = 1.0f;
         if (T == 1) {   // the chosen experts' matrices, picked on the device from the router's list
             GemvRowsParams<AT, WT> p{};
-            p.a = h; p.w = L.wgate; p.w2 = L.wup; p.K = width; p.O = f.ff; p.e = eg; p.bidx = eidx; p.w_bs = (long long)f.ff * width; p.o_bs = f.ff;
-            if (this->template launch_gemv<EPI_GLU, NORM_NONE>(st, p, f.top)) return 1;
+            p.x = x; p.tn = L.n2.view(); p.w = L.wgate; p.w2 = L.wup; p.K = width; p.O = f.ff; p.e = eg; p.bidx = eidx;
+            p.w_bs = (long long)f.ff * width; p.o_bs = f.ff;
+            if (this->template launch_gemv<EPI_GLU, NORM_TANH>(st, p, f.top)) return 1;
             GemvRowsParams<AT, WT> d{};
             d.a = act; d.w = L.wdown; d.K = f.ff; d.O = width; d.e = ed; d.bidx = eidx; d.a_bs = f.ff; d.w_bs = (long long)width * f.ff; d.o_bs = width;
             if (this->template launch_gemv<EPI_STORE, NORM_NONE>(st, d, f.top)) return 1;
@@ -493,7 +507,7 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
             if (this->template matmul_grouped<EPI_STORE>(st, n, f.E, grp, T, act, f.ff, L.wdown, nullptr, f.ff, width, ed)) return 1;
             cp.slot = slot;
         }
-        return launch_k("moe_combine_kernel", st, pdl_now, moe_combine_kernel, dim3(T), dim3(256), 0, cp);
+        return launch_k("moe_combine_kernel", st, pdl_now, moe_combine_kernel, dim3(T, T >= 64 ? 1 : (width + 255) / 256), dim3(256), 0, cp);
     }
 
     int run_layers(cudaStream_t st, int T, const PosSrc& ps, uint32_t pos_hint) override {
@@ -505,11 +519,10 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
         }
         for (size_t li = 0; li < layers.size(); li++) {
             const Layer& L = layers[li];
-            if (norm_rows(st, T, L.n1)) return 1;
             int rc = L.c.kind == MIX_WINDOW ? mixer_window(st, L, T, ps, pos_hint) : (L.c.kind == MIX_LATENT ? mixer_latent(st, L, T, ps, pos_hint) : mixer_delta(st, L, T, ps));
             if (rc) return 1;
             if (L.c.moe.on) {
-                if (norm_rows(st, T, L.n2) || experts(st, L, T)) return 1;
+                if (experts(st, L, T)) return 1;
             }
             if (this->keep_layer(st, li, T)) return 1;
         }

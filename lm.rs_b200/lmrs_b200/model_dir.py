@@ -1,5 +1,6 @@
 """Model folders (config.json + model.safetensors) for the architectures the library opens by name: a writer, the
-tensor table of the Genetar architecture, and random bf16 weights of a given shape for benchmarks and smoke runs.
+tensor tables of the Genetar and Tudatar architectures, and random bf16 weights of a given shape for benchmarks and
+smoke runs.
 
 safetensors layout: 8-byte little-endian header length, that many bytes of JSON (name -> dtype, shape, data_offsets
 relative to the end of the header), then the tensor data.
@@ -68,12 +69,14 @@ def genetar_matmul_flops_per_token(cfg):
     return sum(2 * int(np.prod(shape)) for name, shape, kind in genetar_tensors(cfg) if kind == "matrix")
 
 
-def write_random_genetar(folder, cfg, seed=0):
-    """random bf16 weights, streamed to disk tensor by tensor (a full-size model does not have to fit in host memory twice)"""
+def write_random(folder, cfg, table, seed=0):
+    """random bf16 weights for a tensor table [(name, shape, kind)], streamed to disk tensor by tensor (a full-size model
+    does not have to fit in host memory twice).  kind: matrix (fan-in scaled) | table | ones | scalar | shift | conv | rate |
+    small | zero"""
     os.makedirs(folder, exist_ok=True)
     with open(os.path.join(folder, "config.json"), "w") as f:
         json.dump(cfg, f)
-    table, header, off = genetar_tensors(cfg), {}, 0
+    header, off = {}, 0
     for name, shape, _ in table:
         n = (int(np.prod(shape)) if shape else 1) * 2
         header[name] = {"dtype": "BF16", "shape": list(shape), "data_offsets": [off, off + n]}
@@ -89,9 +92,132 @@ def write_random_genetar(folder, cfg, seed=0):
                 a = 1.0 + 0.1 * rng.standard_normal(n, dtype=np.float32)
             elif kind == "scalar":
                 a = np.array([0.25], np.float32)
+            elif kind == "alpha":
+                a = np.array([0.5], np.float32)
+            elif kind == "shift":
+                a = 0.1 * rng.standard_normal(n, dtype=np.float32)
+            elif kind == "conv":
+                a = 0.5 * rng.standard_normal(n, dtype=np.float32)
+            elif kind == "rate":
+                a = -1.0 + 0.5 * rng.standard_normal(n, dtype=np.float32)
+            elif kind == "small":
+                a = (0.05 + 0.2 * rng.random(n)).astype(np.float32)
+            elif kind == "zero":
+                a = 0.05 * rng.standard_normal(n, dtype=np.float32)
             else:
                 a = rng.standard_normal(n, dtype=np.float32)
                 if kind == "matrix":
                     a *= np.float32(1.0 / math.sqrt(shape[-1]))
             f.write(f32_to_bf16_bits(a).tobytes())
     return folder
+
+
+def write_random_genetar(folder, cfg, seed=0):
+    return write_random(folder, cfg, genetar_tensors(cfg), seed)
+
+
+# ---- Tudatar ---------------------------------------------------------------------------------------------------------------
+def tudatar_config(width, n_layers, vocab, *, heads=16, kv_heads=4, head_dim=64, window=1024, delta_heads=None, delta_dim=None,
+                   conv=4, kv_rank=256, q_rank=768, rot_dim=64, experts=16, top=4, expert_ff=2048, eps=1e-5, logit_scale=1.0,
+                   pattern=("channel_delta", "attention", "channel_delta", "latent_attention"), low_rank=64):
+    """layers cycle through `pattern`; every layer has a routed-expert feed-forward (experts == 0: none)"""
+    layers = []
+    mlp = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top, "scale": 1.0}} if experts else None
+    for i in range(n_layers):
+        kind = pattern[i % len(pattern)]
+        if kind == "channel_delta":
+            h = delta_heads or heads
+            d = delta_dim or head_dim
+            m = {"heads": h, "kv_heads": h, "dim": d, "vdim": d, "conv": conv, "a_rank": low_rank, "g_rank": low_rank}
+        elif kind == "latent_attention":
+            m = {"heads": heads, "dim": head_dim, "rot_dim": rot_dim, "vdim": head_dim, "kv_rank": kv_rank, "q_rank": q_rank,
+                 "scale": 1.0 / math.sqrt(head_dim + rot_dim),
+                 "rot": {"base": 10000.0, "dims": rot_dim, "scaling": {"factor": 8.0, "fast": 32.0, "slow": 1.0, "original": 4096}}}
+        else:
+            m = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": 1.0 / math.sqrt(head_dim),
+                 "mask": {"size": window}}
+        layers.append({"type": kind, "mixer": m, "mlp": mlp})
+    return {"architecture": "Tudatar", "width": width, "vocab": vocab, "norm": {"eps": eps}, "logit_scale": logit_scale, "layers": layers}
+
+
+def tudatar_tensors(cfg):
+    """[(name, shape, kind)] -- the ranks of the delta rule's two low-rank projections are tensor shapes, not configuration:
+    the writer takes them from the hints a_rank / g_rank that tudatar_config leaves in the mixer entry"""
+    w = cfg["width"]
+
+    def norm(n):
+        return [(n, (w,), "ones"), (n + ".b", (w,), "shift"), (n + ".alpha", (), "alpha")]
+    out = [("embed", (cfg["vocab"], w), "table")]
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        out += norm(p + "norm1") + norm(p + "norm1b")
+        q = p + "mix."
+        if L["type"] == "channel_delta":
+            H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            ra, rg = m.get("a_rank", 64), m.get("g_rank", 64)
+            out += [(q + "q", (G * dk, w), "matrix"), (q + "q.conv", (G * dk, m["conv"]), "conv"), (q + "k", (G * dk, w), "matrix"),
+                    (q + "k.conv", (G * dk, m["conv"]), "conv"), (q + "v", (H * dv, w), "matrix"), (q + "v.conv", (H * dv, m["conv"]), "conv"),
+                    (q + "b", (H, w), "matrix"), (q + "A_log", (H,), "rate"), (q + "norm", (dv,), "ones"), (q + "a1", (ra, w), "matrix"),
+                    (q + "a2", (H * dk, ra), "matrix"), (q + "dt_bias", (H * dk,), "shift"), (q + "g1", (rg, w), "matrix"),
+                    (q + "g2", (H * dv, rg), "matrix"), (q + "o", (w, H * dv), "matrix")]
+        elif L["type"] == "latent_attention":
+            H, dn, dr, dv, rk, rq = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            out += [(q + "dq", (rq, w), "matrix"), (q + "dq.norm", (rq,), "ones"), (q + "uq", (H * (dn + dr), rq), "matrix"),
+                    (q + "dkv", (rk + dr, w), "matrix"), (q + "dkv.norm", (rk,), "ones"), (q + "uk", (H * dn, rk), "matrix"),
+                    (q + "uv", (H * dv, rk), "matrix"), (q + "o", (w, H * dv), "matrix")]
+        else:
+            H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            out += [(q + "q", (H * dk, w), "matrix"), (q + "q.b", (H * dk,), "shift"), (q + "k", (G * dk, w), "matrix"),
+                    (q + "k.b", (G * dk,), "shift"), (q + "v", (G * dv, w), "matrix"), (q + "v.b", (G * dv,), "shift"),
+                    (q + "q.norm", (H * dk,), "ones"), (q + "k.norm", (G * dk,), "ones"), (q + "r1", (H,), "small"), (q + "r2", (H,), "small"),
+                    (q + "o", (w, H * dv), "matrix")]
+        if L.get("mlp"):
+            f = L["mlp"]
+            out += norm(p + "norm2") + norm(p + "norm2b")
+            out += [(p + "mlp.router", (f["router"]["experts"], w), "matrix"), (p + "mlp.correction", (f["router"]["experts"],), "zero")]
+            for e in range(f["router"]["experts"]):
+                out += [(f"{p}mlp.e{e}.gate", (f["expert"]["ff"], w), "matrix"), (f"{p}mlp.e{e}.up", (f["expert"]["ff"], w), "matrix"),
+                        (f"{p}mlp.e{e}.down", (w, f["expert"]["ff"]), "matrix")]
+    return out + norm("final.norm") + [("head", (cfg["vocab"], w), "matrix")]
+
+
+def _tudatar_active(cfg, name):
+    """share of a tensor that one token touches: an expert matrix counts top / experts"""
+    if ".mlp.e" in name:
+        f = cfg["layers"][int(name[1:name.index(".")])]["mlp"]["router"]
+        return f["top"] / f["experts"]
+    return 1.0
+
+
+def tudatar_param_bytes(cfg, bytes_per_weight=2):
+    """bytes a decode step streams: every matrix of the mixers once, the chosen experts, one row of the embedding table"""
+    total = 0.0
+    for name, shape, kind in tudatar_tensors(cfg):
+        n = int(np.prod(shape)) if shape else 1
+        total += (shape[1] if kind == "table" else n) * bytes_per_weight * _tudatar_active(cfg, name)
+    return int(total)
+
+
+def tudatar_matmul_flops_per_token(cfg):
+    return int(sum(2 * int(np.prod(shape)) * _tudatar_active(cfg, name) for name, shape, kind in tudatar_tensors(cfg) if kind == "matrix"))
+
+
+def tudatar_mixer_flops(cfg, T):
+    """FLOPs of the sequence mixers' cores over a prompt of T tokens: attention (in the latent space for latent layers, inside the
+    window for windowed ones) and the delta-rule scan (two passes over the state per token)"""
+    total = 0
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        if L["type"] == "channel_delta":
+            total += 6 * m["heads"] * m["dim"] * m["vdim"] * T
+        elif L["type"] == "latent_attention":
+            total += 2 * m["heads"] * (2 * m["kv_rank"] + m["rot_dim"]) * T * (T + 1) // 2
+        else:
+            w = m.get("mask", {}).get("size", 0) or T
+            pairs = T * (T + 1) // 2 if T <= w else w * (w + 1) // 2 + (T - w) * w
+            total += 2 * m["heads"] * (m["dim"] + m["vdim"]) * pairs
+    return total
+
+
+def write_random_tudatar(folder, cfg, seed=0):
+    return write_random(folder, cfg, tudatar_tensors(cfg), seed)
