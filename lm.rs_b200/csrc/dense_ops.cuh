@@ -764,6 +764,7 @@ template <typename AT> __global__ void __launch_bounds__(128) attn_combine_kerne
     for (int c0 = 0; c0 < p.dv; c0 += 32) {
         const int c = c0 + lane;
         float a = 0.0f;
+#pragma unroll 8
         for (int s = 0; s < p.nsplit; s++) {
             const float w = __shfl_sync(0xffffffffu, ws, s);
             if (c < p.dv) a = fmaf(src[(size_t)s * (p.dv + 2) + 2 + c], w, a);

@@ -3,7 +3,9 @@
 //   latent_kv_post_kernel     attention through a shared latent: RMS norm of the query latent and of the key/value latent,
 //                             pairwise rotation of the shared rotated key part, latent + rotated part written to the cache
 //   latent_q_post_kernel      per query head: unrotated part to the operand type (it is multiplied into the latent space
-//                             next), rotated part rotated and placed behind the latent-space part of the query
+//                             next), rotated part rotated and placed behind the latent-space part of the query; or, for the
+//                             per-head form, the whole head [unrotated | rotated] in f32
+//   latent_expand_kernel      per-head keys [up-projected latent | shared rotated part] assembled for all cached positions
 //   qkv_jointnorm_post_kernel q and k RMS-normalised over the WHOLE projection (all heads at once) with a weight, v divided
 //                             by its root mean square per head; k and v written to the cache
 //   delta_pre_kernel          gated delta rule: short causal convolution + SiLU on q, k, v channels (continued from a tail of
@@ -38,6 +40,7 @@ template <typename AT> struct LatentKvPostParams {
     int rot_dims; const float* rot_cos; const float* rot_sin;      // [max_tokens][rot_dims/2], multiplier folded in
     AT* cq_out;                                                   // [T][rq]
     float* cache;                                                 // [max_tokens][rk + dr]
+    AT* cache_op;                                                 // [max_tokens][rk]: the latent again, in the operand type
     PosSrc ps;
 };
 template <typename AT> __global__ void __launch_bounds__(256) latent_kv_post_kernel(const LatentKvPostParams<AT> p) {
@@ -58,7 +61,11 @@ template <typename AT> __global__ void __launch_bounds__(256) latent_kv_post_ker
     ss = block_sum(ss, red);
     inv = 1.0f / sqrtf(ss / (float)p.rk + p.eps);
     float* dst = p.cache + (size_t)pos * (p.rk + p.dr);
-    for (int c = threadIdx.x; c < p.rk; c += blockDim.x) dst[c] = kv[c] * inv * p.wkv[c];
+    for (int c = threadIdx.x; c < p.rk; c += blockDim.x) {
+        const float v = kv[c] * inv * p.wkv[c];
+        dst[c] = v;
+        from_f(p.cache_op[(size_t)pos * p.rk + c], v);
+    }
     if (threadIdx.x < 32) {
         const int half = p.rot_dims / 2;
         rotate_pairs_warp(kv + p.rk, dst + p.rk, p.dr, p.rot_dims, p.rot_cos + (size_t)pos * half, p.rot_sin + (size_t)pos * half, threadIdx.x);
@@ -71,6 +78,7 @@ template <typename AT> struct LatentQPostParams {
     int rot_dims; const float* rot_cos; const float* rot_sin;
     AT* qn_out;               // [T][H * dn]
     float* qabs;              // [T][H * (rk + dr)]: the rotated part goes to columns rk .. rk+dr of each head
+    float* qfull;             // when set instead: [T][H * (dn + dr)], the unrotated part copied, the rotated part rotated
     PosSrc ps;
 };
 template <typename AT> __global__ void __launch_bounds__(128) latent_q_post_kernel(const LatentQPostParams<AT> p) {
@@ -81,11 +89,35 @@ template <typename AT> __global__ void __launch_bounds__(128) latent_q_post_kern
     if (h >= p.H) return;
     const uint32_t pos = pos_of(p.ps) + (uint32_t)t;
     const float* src = p.q + ((size_t)t * p.H + h) * (p.dn + p.dr);
+    const int half = p.rot_dims / 2;
+    if (p.qfull) {
+        float* dst = p.qfull + ((size_t)t * p.H + h) * (p.dn + p.dr);
+        for (int d = lane; d < p.dn; d += 32) dst[d] = src[d];
+        rotate_pairs_warp(src + p.dn, dst + p.dn, p.dr, p.rot_dims, p.rot_cos + (size_t)pos * half, p.rot_sin + (size_t)pos * half, lane);
+        return;
+    }
     AT* qn = p.qn_out + ((size_t)t * p.H + h) * p.dn;
     for (int d = lane; d < p.dn; d += 32) from_f(qn[d], src[d]);
-    const int half = p.rot_dims / 2;
     rotate_pairs_warp(src + p.dn, p.qabs + ((size_t)t * p.H + h) * (p.rk + p.dr) + p.rk, p.dr, p.rot_dims,
                       p.rot_cos + (size_t)pos * half, p.rot_sin + (size_t)pos * half, lane);
+}
+
+// keys per head for positions 0 .. n: kfull[j][h] = [knope[j][h] (dn) | cached rotated part of position j (dr)]
+struct LatentExpandParams {
+    const float* knope;       // [n][H * dn] up-projected latents
+    const float* cache;       // [max_tokens][rk + dr]
+    float* kfull;             // [n][H * (dn + dr)]
+    int H, dn, dr, rk;
+};
+static __global__ void __launch_bounds__(256) latent_expand_kernel(const LatentExpandParams p) {
+    pdl_launch();
+    pdl_wait();
+    const int j = blockIdx.x, dq = p.dn + p.dr;
+    const float* kr = p.cache + (size_t)j * (p.rk + p.dr) + p.rk;
+    for (int e = threadIdx.x; e < p.H * dq; e += blockDim.x) {
+        const int h = e / dq, d = e - h * dq;
+        p.kfull[(size_t)j * p.H * dq + e] = d < p.dn ? p.knope[((size_t)j * p.H + h) * p.dn + d] : kr[d - p.dn];
+    }
 }
 
 // ---- q and k normalised over the whole projection, v per head --------------------------------------------------------------
@@ -311,6 +343,7 @@ static __global__ void __launch_bounds__(DELTA_THREADS) delta_scan_kernel(const 
         const float* gs = ks + DELTA_TB * dkp;
         const float* vs = gs + DELTA_TB * dkp;
         const float* bs = vs + DELTA_TB * cols;
+#pragma unroll 2
         for (int tt = 0; tt < nt; tt++) {
             float kk[DELTA_NR];
             float r0 = 0.0f, r1 = 0.0f, r2 = 0.0f, r3 = 0.0f;

@@ -36,10 +36,12 @@ template <typename AT> __global__ void __launch_bounds__(128) moe_logits_kernel(
     float a = 0.0f;
     if (p.h) {
         const AT* h = p.h + (size_t)t * p.ld;
+#pragma unroll 8
         for (int c = lane; c < p.width; c += 32) a = fmaf(w[c], to_f(h[c]), a);
     } else {
         const float* x = p.x + (size_t)t * p.ld;
         const float alpha = *p.tn.alpha;
+#pragma unroll 8
         for (int c = lane; c < p.width; c += 32) { AT r; from_f(r, tanhnorm_apply(p.tn, alpha, c, x[c])); a = fmaf(w[c], to_f(r), a); }
     }
     a = warp_sum(a);

@@ -6,9 +6,11 @@
 //                       and key channel from a low-rank projection, state S [dk][dv] per head in f32, output RMS-normed per
 //                       head and gated by a second low-rank projection
 //   "latent_attention"  softmax attention whose keys and values are up-projections of one cached latent per token plus one
-//                       rotated key part shared by all heads; queries go through a latent of their own.  It runs in the
-//                       latent space: the up-projection of the keys is multiplied into the query, the attention kernel sees one
-//                       shared key/value head of size kv_rank (+ rot_dim), and the values' up-projection follows it
+//                       rotated key part shared by all heads; queries go through a latent of their own.  Short steps run in
+//                       the latent space: the up-projection of the keys is multiplied into the query, the attention kernel
+//                       sees one shared key/value head of size kv_rank (+ rot_dim), and the values' up-projection follows it.
+//                       Long portions up-project all cached latents to per-head keys and values first (tensor cores) and run
+//                       ordinary multi-head attention over them: a third of the attention arithmetic
 //   "attention"         grouped-head attention with projection biases, q and k RMS-normed over the whole projection, values
 //                       normed per head, a sliding window and a logarithmic distance penalty per head, no rotation
 // and a feed-forward of routed experts (sigmoid router, choice with a correction, normalised weights).  logits =
@@ -87,7 +89,8 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
         float *qnorm = nullptr, *knorm = nullptr, *r1 = nullptr, *r2 = nullptr, *kcache = nullptr, *vcache = nullptr;
         // MIX_LATENT
         float *dq_norm = nullptr, *dkv_norm = nullptr, *lcache = nullptr;
-        WT *wuq = nullptr, *wukT = nullptr, *wuv = nullptr;   // wukT: [H][rk][dn], the keys' up-projection transposed per head
+        AT* lcache_op = nullptr;                               // [max_tokens][rk] the latent in the operand type
+        WT *wuq = nullptr, *wuk = nullptr, *wukT = nullptr, *wuv = nullptr;   // wukT: [H][rk][dn], wuk transposed per head
         const float *rot_cos = nullptr, *rot_sin = nullptr;
         // MIX_DELTA
         float *wconv = nullptr, *tail = nullptr, *a_log = nullptr, *onorm = nullptr, *dt_bias = nullptr, *state = nullptr;
@@ -106,6 +109,9 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
     AT *h = nullptr, *lat = nullptr, *qn = nullptr, *att = nullptr, *att2 = nullptr, *xg = nullptr, *act = nullptr;
     float *rz = nullptr, *proj = nullptr, *qa = nullptr, *qb = nullptr, *fa = nullptr, *fb = nullptr, *beta = nullptr, *part = nullptr, *y = nullptr, *wts = nullptr;
     int *eidx = nullptr, *slot = nullptr, *row_of = nullptr, *grp = nullptr;
+    float *kfull = nullptr, *vfull = nullptr, *knope = nullptr;   // per-head keys and values of all cached positions (long latent-attention portions)
+    int max_kfull = 0, max_vfull = 0, max_knope = 0;
+    int latent_expand_rows = 16;   // portions of at least this many rows take the per-head form
     int max_proj = 0, max_lat = 0, max_qn = 0, max_att = 0, max_att2 = 0, max_qa = 0, max_qb = 0, max_fa = 0, max_fb = 0, max_H = 0,
         max_dv = 0, max_top = 0, max_ff = 0, max_E = 0;
 
@@ -258,7 +264,9 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
                 const int dq = c.dk + c.dr;
                 if (load_stack(st, {{q + "dq", c.rq}, {q + "dkv", c.rk + c.dr}}, width, &L.w_in, &L.in_rows)) return 1;
                 if (load_vec(st, q + "dq.norm", c.rq, &L.dq_norm) || load_vec(st, q + "dkv.norm", c.rk, &L.dkv_norm)) return 1;
-                if (load_stack(st, {{q + "uq", c.H * dq}}, c.rq, &L.wuq, nullptr) || load_stack(st, {{q + "uv", c.H * c.dv}}, c.rk, &L.wuv, nullptr)) return 1;
+                if (load_stack(st, {{q + "uq", c.H * dq}}, c.rq, &L.wuq, nullptr) || load_stack(st, {{q + "uv", c.H * c.dv}}, c.rk, &L.wuv, nullptr) ||
+                    load_stack(st, {{q + "uk", c.H * c.dk}}, c.rk, &L.wuk, nullptr))
+                    return 1;
                 if (need(st, q + "uk", {c.H * c.dk, c.rk}, &t)) return 1;
                 std::vector<float> tr((size_t)c.H * c.rk * c.dk);   // [h][r][d] <- uk[h*dn + d][r]
                 for (int hh = 0; hh < c.H; hh++)
@@ -269,7 +277,8 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
                                 t->dtype == "BF16" ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(t->data)[src]) : reinterpret_cast<const float*>(t->data)[src];
                         }
                 if (dalloc(&L.wukT, tr.size()) || upload_host(tr, L.wukT)) return 1;
-                if (dalloc(&L.lcache, (size_t)max_tokens * (c.rk + c.dr))) return 1;
+                if (dalloc(&L.lcache, (size_t)max_tokens * (c.rk + c.dr)) || dalloc(&L.lcache_op, (size_t)max_tokens * c.rk)) return 1;
+                max_kfull = std::max(max_kfull, c.H * dq); max_vfull = std::max(max_vfull, c.H * c.dv); max_knope = std::max(max_knope, c.H * c.dk);
                 if (c.rot.dims > 0) {
                     std::vector<double> f;
                     double mult;
@@ -412,13 +421,33 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
         if (in_proj(st, L, T)) return 1;
         LatentKvPostParams<AT> kp{};
         kp.in = proj; kp.ld = L.in_rows; kp.rq = c.rq; kp.rk = c.rk; kp.dr = c.dr; kp.wq = L.dq_norm; kp.wkv = L.dkv_norm; kp.eps = info.eps;
-        kp.rot_dims = c.rot.dims; kp.rot_cos = L.rot_cos; kp.rot_sin = L.rot_sin; kp.cq_out = lat; kp.cache = L.lcache; kp.ps = ps;
+        kp.rot_dims = c.rot.dims; kp.rot_cos = L.rot_cos; kp.rot_sin = L.rot_sin; kp.cq_out = lat; kp.cache = L.lcache; kp.cache_op = L.lcache_op; kp.ps = ps;
         if (launch_k("latent_kv_post_kernel", st, pdl_now, latent_kv_post_kernel<AT>, dim3(T), dim3(256), 0, kp)) return 1;
         EpiParams<AT> eq{}; eq.out = qb; eq.ldo = c.H * dq; eq.scale = 1.0f;
         if (this->template matmul<EPI_STORE>(st, T, lat, c.rq, L.wuq, nullptr, c.rq, c.H * dq, eq)) return 1;
         LatentQPostParams<AT> qp{};
         qp.q = qb; qp.H = c.H; qp.dn = c.dk; qp.dr = c.dr; qp.rk = c.rk; qp.rot_dims = c.rot.dims; qp.rot_cos = L.rot_cos; qp.rot_sin = L.rot_sin;
         qp.qn_out = qn; qp.qabs = qa; qp.ps = ps;
+        if (T >= latent_expand_rows && !ps.sp && B::attention_fits(dq, c.dv)) {
+            // per-head form: keys and values of positions 0 .. n up-projected from the cached latents, then plain attention
+            const int n = (int)ps.pos + T;
+            if (!kfull && (dalloc(&kfull, (size_t)max_tokens * max_kfull) || dalloc(&vfull, (size_t)max_tokens * max_vfull) || dalloc(&knope, (size_t)max_tokens * max_knope)))
+                return 1;
+            qp.qfull = qa;
+            if (launch_k("latent_q_post_kernel", st, pdl_now, latent_q_post_kernel<AT>, dim3(T, (c.H + 3) / 4), dim3(128), 0, qp)) return 1;
+            EpiParams<AT> ek{}; ek.out = knope; ek.ldo = c.H * c.dk; ek.scale = 1.0f;
+            if (this->template matmul<EPI_STORE>(st, n, L.lcache_op, c.rk, L.wuk, nullptr, c.rk, c.H * c.dk, ek)) return 1;
+            EpiParams<AT> ev2{}; ev2.out = vfull; ev2.ldo = c.H * c.dv; ev2.scale = 1.0f;
+            if (this->template matmul<EPI_STORE>(st, n, L.lcache_op, c.rk, L.wuv, nullptr, c.rk, c.H * c.dv, ev2)) return 1;
+            LatentExpandParams xp{};
+            xp.knope = knope; xp.cache = L.lcache; xp.kfull = kfull; xp.H = c.H; xp.dn = c.dk; xp.dr = c.dr; xp.rk = c.rk;
+            if (launch_k("latent_expand_kernel", st, pdl_now, latent_expand_kernel, dim3(n), dim3(256), 0, xp)) return 1;
+            AttnRowsParams<AT> p{};
+            p.q = qa; p.kcache = kfull; p.vcache = vfull; p.out = att2;
+            p.T = T; p.H = c.H; p.G = c.H; p.dk = dq; p.dv = c.dv; p.scale = c.scale; p.ps = ps; p.k_ld = c.H * dq; p.v_ld = c.H * c.dv;
+            if (this->attention_launch(st, p, part, pos_hint)) return 1;
+            return out_proj(st, T, att2, c.H * c.dv, L.wo, L.n1b);
+        }
         if (launch_k("latent_q_post_kernel", st, pdl_now, latent_q_post_kernel<AT>, dim3(T, (c.H + 3) / 4), dim3(128), 0, qp)) return 1;
         // the unrotated query part of head z into the latent space: qa[:, z*dl .. z*dl+rk] = qn[:, z*dn ..] . wukT[z]^T
         EpiParams<AT> ea{}; ea.out = qa; ea.ldo = c.H * dl; ea.scale = 1.0f;
@@ -541,6 +570,9 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
         return this->template matmul<EPI_STORE>(st, m, hn, width, head, nullptr, width, vocab, e);
     }
 
+    void set_model_option(const char* name, int value) override {
+        if (!strcmp(name, "latent_expand_rows")) latent_expand_rows = std::max(2, value);
+    }
     // test access: what a layer caches per position.  Windowed attention: K and V rows; latent attention: the latent and the
     // rotated key part (as "k" and "v"); delta-rule layers keep no per-position rows.
     int read_kv(cudaStream_t st, uint32_t layer, uint32_t pos0, uint32_t n, float* k_out, float* v_out) override {

@@ -152,6 +152,26 @@ def test_portions_do_not_change_the_numbers_beyond_rounding(gpu_lib, tmp_path):
     m.close()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_latent_attention_in_the_latent_space_and_per_head(gpu_lib, tmp_path, dtype):
+    """short steps multiply the keys' up-projection into the query, long portions up-project the cached latents: the same
+    numbers either way, for whole prompts and for portions that continue a cache"""
+    cfg = O.make_config([O.latent_layer(mlp=None), O.latent_layer(heads=5, dim=8, rot_dim=6, vdim=10, kv_rank=12, q_rank=20, scaling=None, mlp=None)])
+    toks = tokens_for(cfg, 100, seed=6)
+    W = O.random_weights(cfg, seed=13, gain=2.0)
+    want, _ = O.forward(cfg, W, toks)
+    m = open_model(gpu_lib, tmp_path, cfg, W, dtype)
+    for rows in (1000, 2):   # never per head | always per head (portions of two and more)
+        m.set_option("latent_expand_rows", rows)
+        assert O.rel_rms(m.forward_tokens(toks, 0, list(range(100))), want) < TOL[dtype]
+        at, got = 0, []
+        for c in (3, 61, 2, 33, 1):
+            got.append(m.forward_tokens(toks[at:at + c], at, list(range(c))))
+            at += c
+        assert O.rel_rms(np.concatenate(got), want) < TOL[dtype]
+    m.close()
+
+
 def test_wanted_rows_in_any_order(gpu_lib, tmp_path):
     cfg = mixed_cfg()
     toks = tokens_for(cfg, 40)
