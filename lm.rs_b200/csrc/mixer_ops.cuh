@@ -253,38 +253,47 @@ static __global__ void __launch_bounds__(256) delta_decay_kernel(const DeltaDeca
 }
 
 // The scan.  CTA = (block of state columns, head); a column j of the head's state S [dk][dv] belongs to `lpc` adjacent lanes,
-// lane s of them holding DELTA_NR rows in registers: groups of four consecutive rows, group r4 at rows (r4*lpc + s)*4 .., so a
+// lane s of them holding NR rows in registers: groups of four consecutive rows, group r4 at rows (r4*lpc + s)*4 .., so a
 // lane reads its q, k and decay entries of a token with 16-byte shared-memory loads that do not collide with its neighbours'.
 // Columns never interact: S^T k and S^T q are sums down a column, the rank-one update adds k_i u_j.  Tokens are staged
 // DELTA_TB at a time in shared memory by cp.async (q, k, decays, v, beta), the next block in flight while this one is used;
 // rows beyond dk are zero-filled, so the arithmetic needs no bounds.  Every token costs two passes over the registers and two
 // reductions across the lpc lanes.  The order of every sum is fixed, so a token's result does not depend on the portion it
 // arrives in.  The state is read at the start (zeros when the step starts at position 0) and written back at the end.
-constexpr int DELTA_NR = 16, DELTA_TB = 8, DELTA_THREADS = 128;
+constexpr int DELTA_TB = 8, DELTA_THREADS = 128, DELTA_MAX_DK = 512;
 struct DeltaScanParams {
     const float* qkv; int ld;   // [T][C]: q at 0, k at G*dk, v at 2*G*dk
     const float* decay;         // [T][H*dk]
     const float* beta;          // [T][H]
     float* state;               // [H][dk][dv]
     float* out;                 // [T][H*dv]
-    int T, H, G, dk, dv, lpc;
+    int T, H, G, dk, dv;
     PosSrc ps;
 };
-inline int delta_lanes_per_column(int dk) { int l = 1; while (l * DELTA_NR < dk) l *= 2; return l; }   // dk <= 32 * DELTA_NR
-inline size_t delta_scan_smem(int lpc) { return (size_t)2 * DELTA_TB * (3 * DELTA_NR * lpc + DELTA_THREADS / lpc + 4) * 4; }
+// (rows per lane NR, lanes per column LPC) for a key size: NR * LPC >= dk.  A warp issues dependent instructions only every few
+// cycles, so the split favours many lanes per column (more warps per scheduler, shorter chains) over few
+inline void delta_scan_shape(int dk, int* nr, int* lpc) {
+    if (dk <= 16) { *nr = 16; *lpc = 1; }
+    else if (dk <= 32) { *nr = 16; *lpc = 2; }
+    else if (dk <= 64) { *nr = 8; *lpc = 8; }
+    else if (dk <= 128) { *nr = 8; *lpc = 16; }
+    else if (dk <= 256) { *nr = 8; *lpc = 32; }
+    else { *nr = 16; *lpc = 32; }
+}
+inline size_t delta_scan_smem(int nr, int lpc) { return (size_t)2 * DELTA_TB * (3 * nr * lpc + DELTA_THREADS / lpc + 4) * 4; }
 DN_DEVINL void cp_async4_zfill(void* smem_dst, const void* gsrc, bool valid) {
     const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
     const int n = valid ? 4 : 0;
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
 }
-static __global__ void __launch_bounds__(DELTA_THREADS) delta_scan_kernel(const DeltaScanParams p) {
+template <int NR, int LPC> __global__ void __launch_bounds__(DELTA_THREADS) delta_scan_kernel(const DeltaScanParams p) {
     extern __shared__ __align__(16) float ds_sm[];
     pdl_launch();
     pdl_wait();
-    const int cols = DELTA_THREADS / p.lpc, dkp = DELTA_NR * p.lpc;   // dkp: rows the lanes cover (>= dk, a multiple of 4)
-    const int blk = DELTA_TB * (3 * dkp + cols + 4);                   // floats per staging buffer
+    constexpr int cols = DELTA_THREADS / LPC, dkp = NR * LPC;   // dkp: rows the lanes cover (>= dk, a multiple of 4)
+    constexpr int blk = DELTA_TB * (3 * dkp + cols + 4);                   // floats per staging buffer
     const int h = blockIdx.y, g = h / (p.H / p.G);
-    const int s = threadIdx.x % p.lpc, jl = threadIdx.x / p.lpc, j = blockIdx.x * cols + jl;
+    const int s = threadIdx.x % LPC, jl = threadIdx.x / LPC, j = blockIdx.x * cols + jl;
     const bool col_ok = j < p.dv;
     const uint32_t pos0 = pos_of(p.ps);
     const int vq = 2 * p.G * p.dk;
@@ -325,11 +334,11 @@ static __global__ void __launch_bounds__(DELTA_THREADS) delta_scan_kernel(const 
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     stage(0, 0);
-    float S[DELTA_NR];
+    float S[NR];
     float* sp = p.state + ((size_t)h * p.dk) * p.dv + j;
 #pragma unroll
-    for (int r = 0; r < DELTA_NR; r++) {
-        const int i = ((r >> 2) * p.lpc + s) * 4 + (r & 3);
+    for (int r = 0; r < NR; r++) {
+        const int i = ((r >> 2) * LPC + s) * 4 + (r & 3);
         S[r] = (pos0 > 0 && col_ok && i < p.dk) ? sp[(size_t)i * p.dv] : 0.0f;
     }
     int buf = 0;
@@ -343,13 +352,12 @@ static __global__ void __launch_bounds__(DELTA_THREADS) delta_scan_kernel(const 
         const float* gs = ks + DELTA_TB * dkp;
         const float* vs = gs + DELTA_TB * dkp;
         const float* bs = vs + DELTA_TB * cols;
-#pragma unroll 2
         for (int tt = 0; tt < nt; tt++) {
-            float kk[DELTA_NR];
+            float kk[NR];
             float r0 = 0.0f, r1 = 0.0f, r2 = 0.0f, r3 = 0.0f;
 #pragma unroll
-            for (int r4 = 0; r4 < DELTA_NR / 4; r4++) {
-                const int i = (r4 * p.lpc + s) * 4;
+            for (int r4 = 0; r4 < NR / 4; r4++) {
+                const int i = (r4 * LPC + s) * 4;
                 const float4 g4 = *reinterpret_cast<const float4*>(gs + tt * dkp + i);
                 const float4 k4 = *reinterpret_cast<const float4*>(ks + tt * dkp + i);
                 kk[4 * r4] = k4.x; kk[4 * r4 + 1] = k4.y; kk[4 * r4 + 2] = k4.z; kk[4 * r4 + 3] = k4.w;
@@ -358,12 +366,12 @@ static __global__ void __launch_bounds__(DELTA_THREADS) delta_scan_kernel(const 
                 r2 = fmaf(S[4 * r4 + 2], k4.z, r2); r3 = fmaf(S[4 * r4 + 3], k4.w, r3);
             }
             float rsum = (r0 + r1) + (r2 + r3);
-            for (int o = p.lpc >> 1; o > 0; o >>= 1) rsum += __shfl_xor_sync(0xffffffffu, rsum, o);
+            for (int o = LPC >> 1; o > 0; o >>= 1) rsum += __shfl_xor_sync(0xffffffffu, rsum, o);
             const float u = bs[tt] * (vs[tt * cols + jl] - rsum);
             float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
 #pragma unroll
-            for (int r4 = 0; r4 < DELTA_NR / 4; r4++) {
-                const int i = (r4 * p.lpc + s) * 4;
+            for (int r4 = 0; r4 < NR / 4; r4++) {
+                const int i = (r4 * LPC + s) * 4;
                 const float4 q4 = *reinterpret_cast<const float4*>(qs + tt * dkp + i);
                 S[4 * r4] = fmaf(kk[4 * r4], u, S[4 * r4]); S[4 * r4 + 1] = fmaf(kk[4 * r4 + 1], u, S[4 * r4 + 1]);
                 S[4 * r4 + 2] = fmaf(kk[4 * r4 + 2], u, S[4 * r4 + 2]); S[4 * r4 + 3] = fmaf(kk[4 * r4 + 3], u, S[4 * r4 + 3]);
@@ -371,14 +379,14 @@ static __global__ void __launch_bounds__(DELTA_THREADS) delta_scan_kernel(const 
                 o2 = fmaf(S[4 * r4 + 2], q4.z, o2); o3 = fmaf(S[4 * r4 + 3], q4.w, o3);
             }
             float osum = (o0 + o1) + (o2 + o3);
-            for (int o = p.lpc >> 1; o > 0; o >>= 1) osum += __shfl_xor_sync(0xffffffffu, osum, o);
+            for (int o = LPC >> 1; o > 0; o >>= 1) osum += __shfl_xor_sync(0xffffffffu, osum, o);
             if (s == 0 && col_ok) p.out[(size_t)(t0 + tt) * p.H * p.dv + (size_t)h * p.dv + j] = osum;
         }
     }
     if (col_ok) {
 #pragma unroll
-        for (int r = 0; r < DELTA_NR; r++) {
-            const int i = ((r >> 2) * p.lpc + s) * 4 + (r & 3);
+        for (int r = 0; r < NR; r++) {
+            const int i = ((r >> 2) * LPC + s) * 4 + (r & 3);
             if (i < p.dk) sp[(size_t)i * p.dv] = S[r];
         }
     }

@@ -130,7 +130,7 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
             c.G = (int)m.at("kv_heads").number(c.H);
             c.taps = (int)m.at("conv").number(0);
             if (c.taps < 1 || c.taps > CONV_MAX_TAPS) { error = where + ": conv must be 1 .. " + std::to_string(CONV_MAX_TAPS); return 1; }
-            if (c.dk > 32 * DELTA_NR) { error = where + ": dim above " + std::to_string(32 * DELTA_NR) + " is not supported by the delta-rule kernel"; return 1; }
+            if (c.dk > DELTA_MAX_DK) { error = where + ": dim above " + std::to_string(DELTA_MAX_DK) + " is not supported by the delta-rule kernel"; return 1; }
         } else if (type == "latent_attention") {
             c.kind = MIX_LATENT;
             c.G = 1;
@@ -462,6 +462,12 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
         return out_proj(st, T, att2, c.H * c.dv, L.wo, L.n1b);
     }
 
+    template <int NR, int LPC> int launch_scan(cudaStream_t st, const DeltaScanParams& sp) {
+        constexpr int cols = DELTA_THREADS / LPC;
+        const size_t smem = delta_scan_smem(NR, LPC);
+        if (optin(delta_scan_kernel<NR, LPC>, smem)) return 1;
+        return launch_k("delta_scan_kernel", st, pdl_now, delta_scan_kernel<NR, LPC>, dim3((sp.dv + cols - 1) / cols, sp.H), dim3(DELTA_THREADS), smem, sp);
+    }
     int mixer_delta(cudaStream_t st, const Layer& L, int T, const PosSrc& ps) {
         const LayerCfg& c = L.c;
         const int nqk = c.G * c.dk, nv = c.H * c.dv, C = 2 * nqk + nv;
@@ -491,11 +497,17 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
         if (launch_k("delta_decay_kernel", st, pdl_now, delta_decay_kernel, dim3((dp.n + 255) / 256), dim3(256), 0, dp)) return 1;
         DeltaScanParams sp{};
         sp.qkv = qa; sp.ld = C; sp.decay = araw; sp.beta = beta; sp.state = L.state; sp.out = o;
-        sp.T = T; sp.H = c.H; sp.G = c.G; sp.dk = c.dk; sp.dv = c.dv; sp.lpc = delta_lanes_per_column(c.dk); sp.ps = ps;
-        const int cols = DELTA_THREADS / sp.lpc;
-        const size_t smem = delta_scan_smem(sp.lpc);
-        if (optin(delta_scan_kernel, smem)) return 1;
-        if (launch_k("delta_scan_kernel", st, pdl_now, delta_scan_kernel, dim3((c.dv + cols - 1) / cols, c.H), dim3(DELTA_THREADS), smem, sp)) return 1;
+        sp.T = T; sp.H = c.H; sp.G = c.G; sp.dk = c.dk; sp.dv = c.dv; sp.ps = ps;
+        int nr, lpc;
+        delta_scan_shape(c.dk, &nr, &lpc);
+        int rc = 1;
+        if (nr == 16 && lpc == 1) rc = launch_scan<16, 1>(st, sp);
+        else if (nr == 16 && lpc == 2) rc = launch_scan<16, 2>(st, sp);
+        else if (nr == 8 && lpc == 8) rc = launch_scan<8, 8>(st, sp);
+        else if (nr == 8 && lpc == 16) rc = launch_scan<8, 16>(st, sp);
+        else if (nr == 8 && lpc == 32) rc = launch_scan<8, 32>(st, sp);
+        else rc = launch_scan<16, 32>(st, sp);
+        if (rc) return 1;
         GatedHeadNormParams<AT> gp{};
         gp.o = o; gp.graw = graw; gp.w = L.onorm; gp.eps = info.eps; gp.out = att; gp.rows = T * c.H; gp.dv = c.dv;
         if (launch_k("gated_headnorm_kernel", st, pdl_now, gated_headnorm_kernel<AT>, dim3((gp.rows + 3) / 4), dim3(128), 0, gp)) return 1;

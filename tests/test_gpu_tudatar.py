@@ -79,6 +79,9 @@ ALONE = {
     "delta_ungrouped": dict(layers=[O.delta_layer(heads=3, kv_heads=3, mlp=None)]),
     "delta_one_kv_head": dict(layers=[O.delta_layer(heads=4, kv_heads=1, mlp=None)]),
     "delta_keys_over_several_lanes": dict(layers=[O.delta_layer(heads=2, kv_heads=1, dim=44, vdim=12, mlp=None)]),
+    "delta_keys_over_half_a_warp": dict(layers=[O.delta_layer(heads=2, kv_heads=1, dim=72, vdim=12, mlp=None)]),
+    "delta_keys_over_a_warp": dict(layers=[O.delta_layer(heads=2, kv_heads=2, dim=136, vdim=8, mlp=None)]),
+    "delta_widest_keys": dict(layers=[O.delta_layer(heads=1, kv_heads=1, dim=264, vdim=6, mlp=None)]),
     "delta_wide_values": dict(layers=[O.delta_layer(heads=2, kv_heads=2, dim=8, vdim=136, mlp=None)]),
     "latent": dict(layers=[O.latent_layer(mlp=None)]),
     "latent_plain_frequencies": dict(layers=[O.latent_layer(scaling=None, mlp=None)]),
