@@ -66,6 +66,7 @@ struct LayerCfg {
     int window = 0;                       // MIX_WINDOW
     int taps = 0, ra = 0, rg = 0;         // MIX_DELTA
     int dr = 0, rk = 0, rq = 0;           // MIX_LATENT (dk = unrotated size)
+    bool latent_space_ok = true, per_head_ok = true;
     RotSpec rot;
     MoeCfg moe;
 };
@@ -149,7 +150,10 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
                     c.rot.slow = s.at("slow").number(1.0); c.rot.original = s.at("original").number(4096.0);
                 }
             }
-            if (!B::attention_fits(c.rk + c.dr, c.rk)) { error = where + ": kv_rank " + std::to_string(c.rk) + " needs more shared memory than an SM has for the attention tiles (or is above 256)"; return 1; }
+            // a latent too wide for the attention kernel's tiles is always up-projected to per-head keys and values
+            c.latent_space_ok = B::attention_fits(c.rk + c.dr, c.rk);
+            c.per_head_ok = B::attention_fits(c.dk + c.dr, c.dv);
+            if (!c.latent_space_ok && !c.per_head_ok) { error = where + ": neither kv_rank " + std::to_string(c.rk) + " nor the per-head sizes fit the attention kernel's shared-memory tiles"; return 1; }
         } else if (type == "attention") {
             c.kind = MIX_WINDOW;
             c.G = (int)m.at("kv_heads").number(c.H);
@@ -428,9 +432,12 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
         LatentQPostParams<AT> qp{};
         qp.q = qb; qp.H = c.H; qp.dn = c.dk; qp.dr = c.dr; qp.rk = c.rk; qp.rot_dims = c.rot.dims; qp.rot_cos = L.rot_cos; qp.rot_sin = L.rot_sin;
         qp.qn_out = qn; qp.qabs = qa; qp.ps = ps;
-        if (T >= latent_expand_rows && !ps.sp && B::attention_fits(dq, c.dv)) {
-            // per-head form: keys and values of positions 0 .. n up-projected from the cached latents, then plain attention
-            const int n = (int)ps.pos + T;
+        if (c.per_head_ok && (!c.latent_space_ok || (T >= latent_expand_rows && !ps.sp))) {
+            // per-head form: keys and values of positions 0 .. n up-projected from the cached latents, then plain attention.
+            // A graph-replayed step does not know its position on the host: it up-projects to the end of its 64-position
+            // bucket (rows beyond the position are never read by the attention)
+            int n = (int)ps.pos + T;
+            if (ps.sp) n = (int)(pos_hint / ATT_KT + 1 < (uint32_t)MAX_SPLIT ? std::min<uint32_t>(max_tokens, (pos_hint / ATT_KT + 1) * ATT_KT) : max_tokens);
             if (!kfull && (dalloc(&kfull, (size_t)max_tokens * max_kfull) || dalloc(&vfull, (size_t)max_tokens * max_vfull) || dalloc(&knope, (size_t)max_tokens * max_knope)))
                 return 1;
             qp.qfull = qa;

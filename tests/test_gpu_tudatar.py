@@ -87,6 +87,7 @@ ALONE = {
     "latent_plain_frequencies": dict(layers=[O.latent_layer(scaling=None, mlp=None)]),
     "latent_one_head": dict(layers=[O.latent_layer(heads=1, mlp=None)]),
     "latent_many_heads": dict(layers=[O.latent_layer(heads=20, dim=8, rot_dim=4, vdim=8, kv_rank=16, q_rank=24, mlp=None)]),
+    "latent_too_wide_for_the_latent_space_form": dict(layers=[O.latent_layer(heads=2, dim=8, rot_dim=4, vdim=8, kv_rank=264, q_rank=16, mlp=None)]),
     "latent_equal_sizes": dict(layers=[O.latent_layer(heads=2, dim=16, rot_dim=16, vdim=16, kv_rank=16, q_rank=16, mlp=None)]),
     "window_of_one": dict(layers=[O.window_layer(window=1, mlp=None)]),
     "window_short": dict(layers=[O.window_layer(window=5, mlp=None)]),
