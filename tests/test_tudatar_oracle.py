@@ -182,3 +182,21 @@ def test_write_model_layout(tmp_path):
     assert np.array_equal((bits.astype(np.uint32) << 16).view(np.float32).reshape(24, 3), W["l2.mix.q.conv"].astype(np.float32))
     assert hdr["final.norm.alpha"]["shape"] == []
     assert json.load(open(d + "/config.json"))["layers"][0]["type"] == "latent_attention"
+
+
+def test_the_packaged_writer_names_the_same_tensors():
+    """lmrs_b200.model_dir (random models for benchmarks) and this file's table agree on names and shapes"""
+    from lmrs_b200 import model_dir as md
+    cfg = md.tudatar_config(48, 5, 90, heads=4, kv_heads=2, head_dim=8, window=12, delta_heads=3, delta_dim=16, conv=3, kv_rank=20,
+                            q_rank=28, rot_dim=6, experts=5, top=2, expert_ff=24, low_rank=6)
+    assert [L["type"] for L in cfg["layers"]] == ["channel_delta", "attention", "channel_delta", "latent_attention", "channel_delta"]
+    a = {n: tuple(s) for n, s, _ in md.tudatar_tensors(cfg)}
+    b = {n: tuple(s) for n, s, _ in O.tensor_table(cfg)}
+    assert a == b
+    # the chosen experts' share of the expert matrices, everything else once
+    dense = sum(int(np.prod(s)) for n, s in a.items() if ".mlp.e" not in n and n != "embed")
+    experts = sum(int(np.prod(s)) for n, s in a.items() if ".mlp.e" in n)
+    assert md.tudatar_param_bytes(cfg) == int((dense + a["embed"][1] + experts * 2 / 5) * 2)
+    W = O.random_weights(cfg, seed=1)
+    logits, _ = O.forward(cfg, W, [1, 2, 3])
+    assert logits.shape == (3, 90) and np.isfinite(logits).all()
